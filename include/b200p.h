@@ -272,7 +272,8 @@ enum {
   B200P_GEMM_GLU_CLAMP = 2,  /* rows 2i / 2i+1 of w are gate_i / up_i: y[M,N/2] (dtype) = g * sigmoid(1.702 g) * (u + 1),
                                 g = min(gate, limit), u = clamp(up, -limit, limit)                                  */
   B200P_GEMM_GLU_GELU_TANH = 3, /* same row pairs: y = gelu_tanh(gate) * up                                          */
-  B200P_GEMM_GLU_SILU = 4    /* same row pairs: y = gate * sigmoid(gate) * up                                       */
+  B200P_GEMM_GLU_SILU = 4,   /* same row pairs: y = gate * sigmoid(gate) * up                                       */
+  B200P_GEMM_RELU_SQ = 5     /* y[M,N] (dtype) = max(acc, 0)^2: the hidden units of an ungated feed-forward           */
 };
 /* y = x . w^T, x [M,K] and w [N,K] in `dtype` (row strides ldx / ldw elements), fp32 accumulation; `batch` independent
  * products at element strides stride_x / stride_w / stride_y.  B200P_F32 runs true fp32 FMAs in ascending k.  16-bit calls
@@ -395,9 +396,51 @@ int b200p_moe_route(const float* logits, int64_t ldl, const float* bias, int32_t
                     int32_t* token_of, int64_t M, int E, int top, void* stream);
 /* xs[s, :] = x[token_of[s], :], rows of W elements in `dtype` */
 int b200p_moe_gather(const void* x, const int32_t* token_of, void* xs, int64_t slots, int64_t W, int dtype, void* stream);
-/* y[t, :] = (shared_y ? shared_y[t, :] : 0) + sum_k wts[t, k] * ye[slot_of[t, k], :], all fp32 */
-int b200p_moe_combine(const float* ye, const int32_t* slot_of, const float* wts, const float* shared_y, float* y, int64_t M,
-                      int64_t W, int top, void* stream);
+/* The same outputs from sigmoid scores s = sigmoid(logits): experts are picked by s + correction (NULL: none) among the experts of
+ * the `keep` best of `count` equal groups of neighbouring experts (a group's score = the sum of its two largest picking scores);
+ * wts = the picked experts' s divided by their sum (+ 1e-20), times `scale`.  count == 1 or keep == count: no group limit. */
+int b200p_moe_route_sigmoid(const float* logits, int64_t ldl, const float* correction, int32_t* ids, float* wts, int32_t* seg,
+                            int32_t* slot_of, int32_t* token_of, int64_t M, int E, int top, int count, int keep, float scale,
+                            void* stream);
+/* y[t, :] = (shared_y ? g[t] * shared_y[t, :] : 0) + sum_k wts[t, k] * ye[slot_of[t, k], :], all fp32;
+ * g[t] = sigmoid(shared_gate[t * ldg]) (shared_gate NULL: 1) */
+int b200p_moe_combine(const float* ye, const int32_t* slot_of, const float* wts, const float* shared_y, const float* shared_gate,
+                      int64_t ldg, float* y, int64_t M, int64_t W, int top, void* stream);
+
+/* Selective state-space layer around b200p_delta_scan (B200P_SCAN_ACCUMULATE with KH = groups, dk = state).  proj fp32 [M, ldp]
+ * holds the channels x (H dv) | B (groups state) | C (groups state) from column col_x on and dt (H) at col_dt.  The channels pass a
+ * causal convolution over the sequence (conv_w [C, taps], the last tap the current token's; conv_b [C] or NULL; conv_state
+ * [rows, taps-1, C] carries the inputs of earlier steps: commit it afterwards with b200p_delta_conv_commit on the same columns)
+ * and silu.  dt = softplus(dt + dt_bias); decay [M, H] = exp(-exp(A_log) dt); xs [M, H dv] = x; v = dt x; kn [M, groups state] = B;
+ * qn = C.  All fp32. */
+int b200p_ssm_prep(const float* proj, int64_t ldp, int64_t col_x, int64_t col_dt, const float* conv_w, const float* conv_b,
+                   const float* conv_state, const float* A_log, const float* dt_bias, const int32_t* t_row, const int32_t* t_pos,
+                   const int32_t* t_off, float* xs, float* v, float* kn, float* qn, float* decay, int64_t M, int H, int dv,
+                   int groups, int state, int taps, void* stream);
+/* y = (o + D[h] xs) * silu(z) (z fp32, row stride ldz; D NULL: no skip term); each of `parts` equal runs of the H dv channels is
+ * divided by sqrt(mean(y^2) + eps) over the run; out (dtype, row stride ld_out) = that * norm_w[channel]. */
+int b200p_ssm_out(const float* o, const float* xs, const float* z, int64_t ldz, const float* D, const float* norm_w, void* out,
+                  int64_t ld_out, int64_t M, int H, int dv, int parts, float eps, int dtype, void* stream);
+
+/* Rotated attention with `maps` (1 or 2) score maps per head.  Step 1: proj fp32 [M, ldp] holds q (H x maps x d) at col_q, k
+ * (G x maps x d) at col_k, v (G x dv) at col_v.  In every vector of d the pairs (2i, 2i+1), i < rot_dims / 2, turn by the angle
+ * position * rates[i] (rates fp32, on the device); q_out fp32 [M, H maps d] = that * scale; keys and values go to the caches
+ * [rows, G, Tcap, maps d] / [rows, G, Tcap, dv] (dtype) at (t_row, t_pos). */
+int b200p_rope_attn_prep(const float* proj, int64_t ldp, int64_t col_q, int64_t col_k, int64_t col_v, const float* rates,
+                         int rot_dims, float scale, float* q_out, void* kcache, void* vcache, int64_t Tcap, const int32_t* t_row,
+                         const int32_t* t_pos, int64_t M, int H, int G, int maps, int d, int dv, int dtype, void* stream);
+/* step 2: token t at position p sees j <= p with floor(j / chunk) == floor(p / chunk) (chunk <= 0: all j <= p).  Every map m is a
+ * fp32 softmax attention a_m of its own over the same values; o = a_1 (maps == 1) or a_1 - lambda a_2; with eps >= 0 o is divided
+ * by sqrt(mean_dv(o^2) + eps); out[t, h, :] (dtype, row stride ld_out) = post * o.  Query head h reads key/value head h / (H / G).
+ * cu, rows, nb, max_n describe the ragged batch like b200p_sink_attn; 16-bit caches with d and dv of 32, 64 or 128 run on the
+ * tensor-core tile kernel (decode steps when `workspace` holds their partial sums), everything else on the per-token kernel. */
+int b200p_diff_attn(const float* q, const void* kcache, const void* vcache, int64_t Tcap, const int32_t* t_row, const int32_t* t_pos,
+                    const int32_t* cu, const int32_t* rows, int nb, int max_n, int64_t chunk, int maps, float lambda, float eps,
+                    float post, void* out, int64_t ld_out, int64_t M, int H, int G, int d, int dv, int dtype, void* workspace,
+                    size_t workspace_bytes, void* stream);
+size_t b200p_diff_attn_workspace_bytes(int64_t nb, int H, int maps, int dv);
+/* y[i] *= s for n fp32 values (the logit scale of designs that have one) */
+int b200p_scale(float* y, int64_t n, float s, void* stream);
 
 /* Latent attention, step 1.  proj fp32 [M, ldp] = [down-projected query (q_rank) | down-projected key/value (kv_rank)].
  * cq_out [M, q_rank] (dtype) = rms_norm(query part) * wq; the key/value part, rms_norm * wkv, is written to

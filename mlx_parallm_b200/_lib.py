@@ -89,7 +89,17 @@ SIGNATURES = {
     "b200p_sink_attn_tiles_supported": (_i32, [_i32, _i32, _i32]),
     "b200p_moe_route": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp]),
     "b200p_moe_gather": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp]),
-    "b200p_moe_combine": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _vp]),
+    "b200p_moe_route_sigmoid": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f32, _vp]),
+    "b200p_moe_combine": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i32, _vp]),
+    "b200p_ssm_prep": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32,
+                              _i32, _i32, _i32, _vp]),
+    "b200p_ssm_out": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _f32, _i32, _vp]),
+    "b200p_rope_attn_prep": (_i32, [_vp, _i64, _i64, _i64, _i64, _vp, _i32, _f32, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32,
+                                    _i32, _i32, _i32, _vp]),
+    "b200p_diff_attn": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i32, _i32, _i64, _i32, _f32, _f32, _f32, _vp, _i64, _i64, _i32,
+                               _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
+    "b200p_diff_attn_workspace_bytes": (_sz, [_i64, _i32, _i32, _i32]),
+    "b200p_scale": (_i32, [_vp, _i64, _f32, _vp]),
     "b200p_latent_prep": (_i32, [_vp, _i64, _i32, _i32, _vp, _vp, _f32, _vp, _vp, _i64, _vp, _vp, _i64, _i32, _vp]),
     "b200p_latent_attn": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, _i64, _i32, _i32, _i64, _f32, _i32, _vp]),
     "b200p_latent_attn_set_groups": (_i32, [_i32]),
@@ -104,8 +114,15 @@ SIGNATURES = {
 UNIT_SETS = {
     "sequence": ("runtime", "dense_gemm", "dense_gemm_tc", "ragged", "delta_rule", "latent_attn", "sampler"),
     "sequence_moe": ("runtime", "dense_gemm", "dense_gemm_tc", "ragged", "delta_rule", "sink_attn", "moe", "sampler"),
+    "sequence_ssm": ("runtime", "dense_gemm", "dense_gemm_tc", "ragged", "delta_rule", "ssm", "diff_attn", "moe", "sampler"),
 }
-GEMM_STORE, GEMM_STORE_F32, GEMM_GLU_CLAMP, GEMM_GLU_GELU_TANH, GEMM_GLU_SILU = 0, 1, 2, 3, 4
+GEMM_STORE, GEMM_STORE_F32, GEMM_GLU_CLAMP, GEMM_GLU_GELU_TANH, GEMM_GLU_SILU, GEMM_RELU_SQ = 0, 1, 2, 3, 4, 5
+
+
+def gemm_is_gated(epilogue: int) -> bool:
+    """Epilogues that read (gate, up) row pairs and write half as many columns."""
+    return GEMM_GLU_CLAMP <= epilogue <= GEMM_GLU_SILU
+
 SCAN_DELTA, SCAN_DELTA_CHANNEL, SCAN_ACCUMULATE = 0, 1, 2
 GATE_SILU, GATE_SIGMOID = 0, 1
 

@@ -72,7 +72,15 @@ __device__ __forceinline__ float warp_max(float v) {
 __device__ __forceinline__ float gelu_tanh_unit(float z) {
   return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
-__device__ __forceinline__ bool gemm_epi_is_glu(int epi) { return epi >= B200P_GEMM_GLU_CLAMP; }
+__device__ __forceinline__ bool gemm_epi_is_glu(int epi) { return epi >= B200P_GEMM_GLU_CLAMP && epi <= B200P_GEMM_GLU_SILU; }
+// value stored by the ungated epilogues that write the storage type: the accumulator itself, or an activation of it
+__device__ __forceinline__ float gemm_store_act(float v, int epi) {
+  if (epi == B200P_GEMM_RELU_SQ) {
+    v = fmaxf(v, 0.f);
+    return v * v;
+  }
+  return v;
+}
 __device__ __forceinline__ float glu_unit(float gate, float up, int epi, float limit) {
   if (epi == B200P_GEMM_GLU_CLAMP) {
     const float g = fminf(gate, limit);

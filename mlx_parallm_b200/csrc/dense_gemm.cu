@@ -34,10 +34,10 @@ __device__ __forceinline__ void gemm_store_pair(void* y, int64_t row_off, int64_
     float* p = reinterpret_cast<float*>(y) + row_off;
     if (n < N) p[n] = v0;
     if (n + 1 < N) p[n + 1] = v1;
-  } else if (epi == B200P_GEMM_STORE) {
+  } else if (!gemm_epi_is_glu(epi)) {
     T* p = reinterpret_cast<T*>(y) + row_off;
-    if (n < N) p[n] = Tr<T>::from_f(v0);
-    if (n + 1 < N) p[n + 1] = Tr<T>::from_f(v1);
+    if (n < N) p[n] = Tr<T>::from_f(gemm_store_act(v0, epi));
+    if (n + 1 < N) p[n + 1] = Tr<T>::from_f(gemm_store_act(v1, epi));
   } else {  // gated units: v0 = gate, v1 = up of hidden unit n / 2
     if (n + 1 < N) reinterpret_cast<T*>(y)[row_off + (n >> 1)] = Tr<T>::from_f(glu_unit(v0, v1, epi, limit));
   }
@@ -435,8 +435,8 @@ extern "C" int b200p_gemm_grouped(const void* x, const void* w, void* y, const i
   B200P_REQUIRE(x && w && y && seg, B200P_ERR_ARG, "null pointer");
   B200P_REQUIRE(total_rows >= max_rows, B200P_ERR_ARG, "x has fewer rows than a group may have");
   B200P_REQUIRE(max_rows >= 0 && N > 0 && K > 0 && groups > 0 && groups < 65536 && ldx >= K && ldw >= K, B200P_ERR_ARG, "bad GEMM shape");
-  B200P_REQUIRE(epilogue >= B200P_GEMM_STORE && epilogue <= B200P_GEMM_GLU_SILU, B200P_ERR_ARG, "unknown epilogue %d", epilogue);
-  B200P_REQUIRE(epilogue < B200P_GEMM_GLU_CLAMP || N % 2 == 0, B200P_ERR_ARG, "the gated epilogue needs gate / up row pairs");
+  B200P_REQUIRE(epilogue >= B200P_GEMM_STORE && epilogue <= B200P_GEMM_RELU_SQ, B200P_ERR_ARG, "unknown epilogue %d", epilogue);
+  B200P_REQUIRE(epilogue < B200P_GEMM_GLU_CLAMP || epilogue > B200P_GEMM_GLU_SILU || N % 2 == 0, B200P_ERR_ARG, "the gated epilogue needs gate / up row pairs");
   B200P_REQUIRE((max_rows + 63) / 64 < 65536, B200P_ERR_ARG, "grid too large");
   if (max_rows == 0) return B200P_OK;
   cudaStream_t st = (cudaStream_t)stream;
@@ -467,8 +467,8 @@ extern "C" int b200p_gemm(const void* x, const void* w, void* y, int64_t M, int6
   using namespace b200p;
   B200P_REQUIRE(x && w && y, B200P_ERR_ARG, "null pointer");
   B200P_REQUIRE(M >= 0 && N > 0 && K > 0 && batch > 0 && ldx >= K && ldw >= K, B200P_ERR_ARG, "bad GEMM shape");
-  B200P_REQUIRE(epilogue >= B200P_GEMM_STORE && epilogue <= B200P_GEMM_GLU_SILU, B200P_ERR_ARG, "unknown epilogue %d", epilogue);
-  B200P_REQUIRE(epilogue < B200P_GEMM_GLU_CLAMP || N % 2 == 0, B200P_ERR_ARG, "the gated epilogue needs gate / up row pairs");
+  B200P_REQUIRE(epilogue >= B200P_GEMM_STORE && epilogue <= B200P_GEMM_RELU_SQ, B200P_ERR_ARG, "unknown epilogue %d", epilogue);
+  B200P_REQUIRE(epilogue < B200P_GEMM_GLU_CLAMP || epilogue > B200P_GEMM_GLU_SILU || N % 2 == 0, B200P_ERR_ARG, "the gated epilogue needs gate / up row pairs");
   B200P_REQUIRE((M + 63) / 64 < 65536 && batch < 65536, B200P_ERR_ARG, "grid too large");
   if (M == 0) return B200P_OK;
   cudaStream_t st = (cudaStream_t)stream;

@@ -96,22 +96,25 @@ __device__ __forceinline__ void gemm_tc_store32(const GemmTcParams& p, int64_t r
       for (int i = 0; i < 32; ++i)
         if (n0 + i < p.N) dst[i] = v[i];
     }
-  } else if (p.epi == B200P_GEMM_STORE) {
+  } else if (!gemm_epi_is_glu(p.epi)) {
+    float a[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) a[i] = gemm_store_act(v[i], p.epi);
     T* dst = reinterpret_cast<T*>(p.y) + row_off + n0;
     if (p.vec_ok && n0 + 32 <= p.N) {
 #pragma unroll
       for (int i = 0; i < 32; i += 8) {
         uint4 u;
-        u.x = pack2<T>(v[i], v[i + 1]);
-        u.y = pack2<T>(v[i + 2], v[i + 3]);
-        u.z = pack2<T>(v[i + 4], v[i + 5]);
-        u.w = pack2<T>(v[i + 6], v[i + 7]);
+        u.x = pack2<T>(a[i], a[i + 1]);
+        u.y = pack2<T>(a[i + 2], a[i + 3]);
+        u.z = pack2<T>(a[i + 4], a[i + 5]);
+        u.w = pack2<T>(a[i + 6], a[i + 7]);
         *reinterpret_cast<uint4*>(dst + i) = u;
       }
     } else {
 #pragma unroll
       for (int i = 0; i < 32; ++i)
-        if (n0 + i < p.N) dst[i] = Tr<T>::from_f(v[i]);
+        if (n0 + i < p.N) dst[i] = Tr<T>::from_f(a[i]);
     }
   } else {  // gated units: columns 2i / 2i+1 are gate_i / up_i
     float a[16];
@@ -165,7 +168,7 @@ __device__ __forceinline__ void gemm_tc_store32_trans(const GemmTcParams& p, int
     T* dst = reinterpret_cast<T*>(p.y) + z_off + n;
 #pragma unroll
     for (int i = 0; i < 32; ++i)
-      if (tok0 + i < p.N) dst[(tok0 + i) * p.ldy] = Tr<T>::from_f(v[i]);
+      if (tok0 + i < p.N) dst[(tok0 + i) * p.ldy] = Tr<T>::from_f(gemm_store_act(v[i], p.epi));
   }
 }
 

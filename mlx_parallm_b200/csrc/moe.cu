@@ -1,8 +1,10 @@
 // Routed mixture of experts over a packed token batch:
 //   moe_route_kernel    fp32 router logits (+ bias) -> the `top` largest per token and the softmax over those alone   (per token)
+//   moe_route_sigmoid_kernel  scores = sigmoid(logits); experts picked by score + correction inside the best expert groups;
+//                       weights = the picked experts' scores over their sum, times a scale                              (per token)
 //   moe_plan_kernel     tokens counted per expert, segment offsets, a slot for every (token, choice)                 (one CTA)
 //   moe_gather_kernel   activation rows copied into slot order, so that an expert's rows are contiguous              (per slot)
-//   moe_combine_kernel  y[t] = shared[t] + sum_k weight[t, k] * expert_out[slot(t, k)], in the order of the choices   (per token)
+//   moe_combine_kernel  y[t] = gate[t] shared[t] + sum_k weight[t, k] * expert_out[slot(t, k)], in the order of the choices   (per token)
 // The experts themselves are two grouped GEMMs (b200p_gemm_grouped) over the segments.  Every launch has the same shape whatever
 // the routing, so a decode step with experts sits in a captured graph.
 #include "common.cuh"
@@ -51,6 +53,84 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ldl, 
   }
 }
 
+// One warp per token.  s_e = sigmoid(z_e); picking score c_e = s_e + correction_e.  The experts form `count` groups of
+// neighbours; a group's score is the sum of its two largest picking scores (its only one for groups of one expert); only the
+// experts of the `keep` best groups can be picked (the others count as -inf, since picking scores may be negative).  The `top`
+// largest picking scores win, ties to the smaller index; weights w_k = s_k / (sum of the picked s + 1e-20) * scale.
+__global__ void moe_route_sigmoid_kernel(const float* __restrict__ logits, int64_t ldl, const float* __restrict__ correction,
+                                         int32_t* __restrict__ ids, float* __restrict__ wts, int64_t M, int E, int top, int count,
+                                         int keep, float scale) {
+  extern __shared__ float mr_sm[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= M) return;
+  float* sc = mr_sm + (size_t)warp * (2 * E + count);     // scores
+  float* pick = sc + E;                                    // picking scores, -inf once masked or taken
+  float* gs = pick + E;                                    // group scores
+  for (int e = lane; e < E; e += 32) {
+    const float s = 1.f / (1.f + expf(-logits[t * ldl + e]));
+    sc[e] = s;
+    pick[e] = s + (correction ? correction[e] : 0.f);
+  }
+  __syncwarp();
+  if (count > 1 && keep < count) {
+    const int per = E / count;
+    for (int g = lane; g < count; g += 32) {
+      float a = -INFINITY, b = -INFINITY;                  // the two largest of the group
+      for (int i = 0; i < per; ++i) {
+        const float v = pick[g * per + i];
+        if (v > a) { b = a; a = v; }
+        else if (v > b) b = v;
+      }
+      gs[g] = per > 1 ? a + b : a;
+    }
+    __syncwarp();
+    // drop the count - keep worst groups: repeatedly the smallest score, ties dropping the larger index first
+    for (int r = 0; r < count - keep; ++r) {
+      float worst = INFINITY;
+      int wg = -1;
+      for (int g = lane; g < count; g += 32) {
+        const float v = gs[g];
+        if (v == v && (v < worst || (v == worst && g > wg))) { worst = v; wg = g; }      // NaN marks a dropped group
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ow = __shfl_xor_sync(0xffffffffu, worst, o);
+        const int og = __shfl_xor_sync(0xffffffffu, wg, o);
+        if (og >= 0 && (wg < 0 || ow < worst || (ow == worst && og > wg))) { worst = ow; wg = og; }
+      }
+      if (lane == 0) gs[wg] = __int_as_float(0x7fc00000);
+      for (int i = lane; i < per; i += 32) pick[wg * per + i] = -INFINITY;
+      __syncwarp();
+    }
+  }
+  float den = 0.f, mine = 0.f;
+  int my_id = 0;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int be = E;
+    for (int e = lane; e < E; e += 32)
+      if (pick[e] > best) { best = pick[e]; be = e; }                  // ascending e within a lane: ties keep the smallest index
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (ob > best || (ob == best && oe < be)) { best = ob; be = oe; }
+    }
+    if (be >= E) be = 0;                                               // fewer candidates than picks: cannot happen with keep * per >= top
+    const float s = sc[be];
+    den += s;
+    if (lane == k) { mine = s; my_id = be; }
+    __syncwarp();
+    if (lane == 0) pick[be] = -INFINITY;
+    __syncwarp();
+  }
+  if (lane < top) {
+    ids[t * top + lane] = my_id;
+    wts[t * top + lane] = mine / (den + 1e-20f) * scale;
+  }
+}
+
 __global__ void moe_plan_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ seg, int32_t* __restrict__ slot_of,
                                 int32_t* __restrict__ token_of, int64_t n, int E, int top) {
   extern __shared__ int32_t cnt[];               // [E] counts, then [E] cursors
@@ -90,8 +170,10 @@ __global__ void moe_gather_kernel(const T* __restrict__ x, const int32_t* __rest
 }
 
 __global__ void moe_combine_kernel(const float* __restrict__ ye, const int32_t* __restrict__ slot_of, const float* __restrict__ wts,
-                                   const float* __restrict__ shared_y, float* __restrict__ y, int64_t W, int top) {
+                                   const float* __restrict__ shared_y, const float* __restrict__ shared_gate, int64_t ldg,
+                                   float* __restrict__ y, int64_t W, int top) {
   const int64_t t = blockIdx.x;
+  const float sg = shared_gate ? 1.f / (1.f + expf(-shared_gate[t * ldg])) : 1.f;
   __shared__ int32_t sl[MOE_MAX_TOP];
   __shared__ float wt[MOE_MAX_TOP];
   if (threadIdx.x < top) {
@@ -102,7 +184,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ ye, const int32_t* 
   for (int64_t c = threadIdx.x; c < W; c += blockDim.x) {
     float a = 0.f;
     for (int k = 0; k < top; ++k) a = fmaf(wt[k], ye[(int64_t)sl[k] * W + c], a);
-    if (shared_y) a += shared_y[t * W + c];
+    if (shared_y) a = fmaf(sg, shared_y[t * W + c], a);
     y[t * W + c] = a;
   }
 }
@@ -125,6 +207,30 @@ extern "C" int b200p_moe_route(const float* logits, int64_t ldl, const float* bi
   return B200P_OK;
 }
 
+extern "C" int b200p_moe_route_sigmoid(const float* logits, int64_t ldl, const float* correction, int32_t* ids, float* wts,
+                                       int32_t* seg, int32_t* slot_of, int32_t* token_of, int64_t M, int E, int top, int count,
+                                       int keep, float scale, void* stream) {
+  B200P_REQUIRE(logits && ids && wts && seg && slot_of && token_of, B200P_ERR_ARG, "null pointer");
+  B200P_REQUIRE(E > 0 && E <= 32 * MOE_MAX_PER_LANE && top > 0 && top <= E && top <= MOE_MAX_TOP, B200P_ERR_ARG,
+                "experts in [1, %d] and top in [1, min(experts, %d)]", 32 * MOE_MAX_PER_LANE, MOE_MAX_TOP);
+  B200P_REQUIRE(count >= 1 && E % count == 0 && keep >= 1 && keep <= count && (int64_t)keep * (E / count) >= top, B200P_ERR_ARG,
+                "expert groups: equal groups, 1 <= keep <= count, and the kept groups hold at least `top` experts");
+  if (M == 0) return B200P_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int warps = 4;
+  const size_t smem = (size_t)warps * (2 * E + count) * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(moe_route_sigmoid_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(moe_route_sigmoid_kernel)");
+  }
+  moe_route_sigmoid_kernel<<<(unsigned)((M + warps - 1) / warps), warps * 32, smem, st>>>(logits, ldl, correction, ids, wts, M, E, top,
+                                                                                           count, keep, scale);
+  B200P_LAUNCH_CHECK("moe_route_sigmoid_kernel");
+  moe_plan_kernel<<<1, 1024, 2 * E * sizeof(int32_t), st>>>(ids, seg, slot_of, token_of, M * top, E, top);
+  B200P_LAUNCH_CHECK("moe_plan_kernel");
+  return B200P_OK;
+}
+
 extern "C" int b200p_moe_gather(const void* x, const int32_t* token_of, void* xs, int64_t slots, int64_t W, int dtype, void* stream) {
   B200P_REQUIRE(x && token_of && xs && W > 0, B200P_ERR_ARG, "null pointer");
   if (slots == 0) return B200P_OK;
@@ -134,11 +240,11 @@ extern "C" int b200p_moe_gather(const void* x, const int32_t* token_of, void* xs
   return B200P_OK;
 }
 
-extern "C" int b200p_moe_combine(const float* ye, const int32_t* slot_of, const float* wts, const float* shared_y, float* y,
-                                 int64_t M, int64_t W, int top, void* stream) {
+extern "C" int b200p_moe_combine(const float* ye, const int32_t* slot_of, const float* wts, const float* shared_y,
+                                 const float* shared_gate, int64_t ldg, float* y, int64_t M, int64_t W, int top, void* stream) {
   B200P_REQUIRE(ye && slot_of && wts && y && W > 0 && top > 0 && top <= MOE_MAX_TOP, B200P_ERR_ARG, "null pointer or bad top");
   if (M == 0) return B200P_OK;
-  moe_combine_kernel<<<(unsigned)M, W >= 1024 ? 256 : 128, 0, (cudaStream_t)stream>>>(ye, slot_of, wts, shared_y, y, W, top);
+  moe_combine_kernel<<<(unsigned)M, W >= 1024 ? 256 : 128, 0, (cudaStream_t)stream>>>(ye, slot_of, wts, shared_y, shared_gate, ldg, y, W, top);
   B200P_LAUNCH_CHECK("moe_combine_kernel");
   return B200P_OK;
 }

@@ -247,3 +247,18 @@ extern "C" int b200p_token_gate(const float* gate, const void* table, const int3
   B200P_LAUNCH_CHECK("token_gate_kernel");
   return B200P_OK;
 }
+
+namespace b200p {
+__global__ void scale_kernel(float* __restrict__ y, int64_t n, float s) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) y[i] *= s;
+}
+}  // namespace b200p
+
+extern "C" int b200p_scale(float* y, int64_t n, float s, void* stream) {
+  B200P_REQUIRE(y || n == 0, B200P_ERR_ARG, "null pointer");
+  if (n == 0) return B200P_OK;
+  b200p::scale_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(y, n, s);
+  B200P_LAUNCH_CHECK("scale_kernel");
+  return B200P_OK;
+}

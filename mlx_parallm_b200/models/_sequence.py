@@ -12,15 +12,24 @@ layers mix a recurrent state with windowed attention over a shared low-rank late
     DecayLinearAttention    S <- lambda S + k v^T with constant per-head decays      b200p_linear_attn_prep / b200p_delta_scan / _out
     SideBySideMixer         several of the above on one input, one fused in- and     b200p_gemm
                             out-projection, a scale per branch
+    StateSpaceMixer         short convolution + selective state-space recurrence     b200p_ssm_prep / b200p_delta_scan / b200p_ssm_out
+                            (scalar decay per head and token), gated group norm
+    DifferentialAttention   grouped-head attention with two score maps per head      b200p_rope_attn_prep / b200p_diff_attn
+                            whose outputs are subtracted, partial pairwise rotation,
+                            position chunks
     GatedFF                 W_down (act(W_gate x) * W_up x), act in the epilogue     b200p_gemm (fused epilogue)
-    RoutedExperts           top-k routed GatedFF experts + a shared one             b200p_moe_* / b200p_gemm_grouped
+    ActivatedFF             W_down act(W_up x), act in the epilogue                  b200p_gemm (fused epilogue)
+    RoutedExperts           top-k routed GatedFF experts + a shared one; softmax     b200p_moe_* / b200p_gemm_grouped
+                            over the chosen logits, or sigmoid scores picked inside
+                            the best expert groups with a gated shared expert
     LatentAttention         queries and keys/values through low-rank latents,       b200p_latent_prep / b200p_latent_attn
                             sliding window, optional sharing of another layer's latents
     ClampedGLU              g * sigmoid(1.702 g) * (u + 1) on clamped gate / up      b200p_gemm (fused epilogue)
     TokenSideInput          a small per-layer table indexed by the token, gated      b200p_token_gate
     SequenceModel           the layer chain over a ragged batch: norm -> sublayer -> norm -> residual (b200p_norm_add_norm), or
-                            one norm feeding a mixer and a feed-forward that are added together, with an optional span of
-                            layers that runs several times on the same weights (b200p_residual_add_norm)
+                            one norm feeding a mixer and a feed-forward that are added together, or a norm before each of the
+                            two, with an optional span of layers that runs several times on the same weights
+                            (b200p_residual_add_norm)
 
 A step is a ragged batch: entry e brings ``counts[e]`` tokens for cache row ``rows[e]``; prompts of different lengths are
 packed back to back (no padding), decode steps bring one token per live row.  Every kernel works from the per-token plan
@@ -36,7 +45,9 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from .. import ops
-from .._lib import (GATE_SIGMOID, GATE_SILU, GEMM_GLU_CLAMP, GEMM_GLU_GELU_TANH, GEMM_GLU_SILU, GEMM_STORE, GEMM_STORE_F32,
+import math
+
+from .._lib import (GATE_SIGMOID, GATE_SILU, GEMM_GLU_CLAMP, GEMM_GLU_GELU_TANH, GEMM_GLU_SILU, GEMM_RELU_SQ, GEMM_STORE, GEMM_STORE_F32,
                     SCAN_ACCUMULATE, SCAN_DELTA, SCAN_DELTA_CHANNEL)
 from .base import BatchedKVCache, DeltaRuleState, LatentKVCache, RowState, StateGroup, TokenState
 
@@ -316,6 +327,134 @@ class SideBySideMixer:
         return self.o_proj(mix, GEMM_STORE_F32, out=y_out)
 
 
+class StateSpaceMixer:
+    """Selective state-space layer with a scalar decay per head and token.  One projection gives [z | x | B | C | dt]
+    (inner = heads * vdim channels of z and x, groups * state of B and C, heads of dt).  x, B, C pass a causal convolution of
+    ``taps`` taps with bias and silu; dt = softplus(dt + dt_bias).  Per head (reading the B / C of group h // (heads // groups))
+    the fp32 state S [state, vdim] goes S <- exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x.  Then y * silu(z), an rms norm
+    over each of ``norm_groups`` equal runs of the channels, a weight per channel, the output projection.  The recurrence is the
+    plain-accumulation mode of the delta-rule scan (k = B, q = C, v = dt x)."""
+
+    def __init__(self, width: int, heads: int, vdim: int, state: int, groups: int, norm_groups: int, taps: int, eps: float):
+        if heads % groups or (heads * vdim) % norm_groups:
+            raise ValueError("heads must be a multiple of groups and the channels a multiple of norm_groups")
+        self.width, self.heads, self.vdim, self.state, self.groups, self.norm_groups = width, heads, vdim, state, groups, norm_groups
+        self.taps, self.eps = taps, eps
+        self.inner = heads * vdim
+        self.c_bc = groups * state
+        self.conv_channels = self.inner + 2 * self.c_bc
+        self.col_x = self.inner
+        self.col_dt = self.inner + self.conv_channels
+        self.n_proj = self.col_dt + heads
+        self.in_proj = Linear(width, self.n_proj)
+        self.o_proj = Linear(self.inner, width)
+        self.conv_w = self.conv_b = self.A_log = self.dt_bias = self.D = self.norm_w = None      # fp32
+
+    def new_state(self, batch_size: int) -> RowState:
+        return DeltaRuleState(self.heads, self.state, self.vdim, self.conv_channels, self.taps, batch_size)
+
+    def reserve(self, s: Scratch, dt):
+        s.reserve("proj", torch.float32, self.n_proj)
+        s.reserve("qn", torch.float32, self.c_bc)
+        s.reserve("kn", torch.float32, self.c_bc)
+        s.reserve("v", torch.float32, self.inner)
+        s.reserve("xs", torch.float32, self.inner)
+        s.reserve("decay", torch.float32, self.heads)
+        s.reserve("o", torch.float32, self.inner)
+        s.reserve("mix", dt, self.inner)
+
+    def __call__(self, x, y_out, st: DeltaRuleState, plan: dict, s: Scratch, caches):
+        M, dt, f32 = x.shape[0], x.dtype, torch.float32
+        proj = self.in_proj(x, GEMM_STORE_F32, out=s.get("proj", f32, M, self.n_proj))
+        qn, kn = s.get("qn", f32, M, self.c_bc), s.get("kn", f32, M, self.c_bc)
+        v, xs, o = s.get("v", f32, M, self.inner), s.get("xs", f32, M, self.inner), s.get("o", f32, M, self.inner)
+        decay = s.get("decay", f32, M, self.heads)
+        ops.ssm_prep(proj, self.col_x, self.col_dt, self.conv_w, self.conv_b, st.conv, self.A_log, self.dt_bias, plan["t_row"],
+                     plan["t_pos"], plan["t_off"], xs, v, kn, qn, decay, self.heads, self.vdim, self.groups, self.state, self.taps)
+        ops.delta_conv_commit(proj[:, self.col_x:self.col_dt], st.conv, plan["cu"], plan["rows"], plan["nb"], self.conv_channels, self.taps)
+        ops.delta_scan(qn, kn, v, None, decay, st.state, plan["cu"], plan["rows"], plan["lengths"], o, plan["nb"], self.heads,
+                       self.groups, self.state, self.vdim, SCAN_ACCUMULATE)
+        mix = s.get("mix", dt, M, self.inner)
+        ops.ssm_out(o, xs, proj[:, :self.inner], self.D, self.norm_w, mix, self.heads, self.vdim, self.norm_groups, self.eps)
+        return self.o_proj(mix, GEMM_STORE_F32, out=y_out)
+
+
+def rotary_rates(dims: int, base: float, scaling: Optional[dict] = None) -> List[float]:
+    """Angle per position of the pairs (2i, 2i+1), i < dims / 2: f_i = base^(-2i / dims).  ``scaling`` (factor, low, high,
+    original) slows the long wavelengths down: with l = 2 pi / f, f stays where l < original / high, becomes f / factor where
+    l > original / low, and is blended linearly in between by s = (original / l - low) / (high - low)."""
+    rates = [float(base) ** (-2.0 * i / dims) for i in range(dims // 2)]
+    if not scaling:
+        return rates
+    factor, low, high, original = (float(scaling[k]) for k in ("factor", "low", "high", "original"))
+    out = []
+    for f in rates:
+        wavelength = 2.0 * math.pi / f
+        if wavelength < original / high:
+            out.append(f)
+        elif wavelength > original / low:
+            out.append(f / factor)
+        else:
+            blend = (original / wavelength - low) / (high - low)
+            out.append((1.0 - blend) * f / factor + blend * f)
+    return out
+
+
+class DifferentialAttention:
+    """Causal attention with ``heads`` query heads over ``kv_heads`` key/value heads and ``maps`` (1 or 2) score maps per head:
+    q holds heads x maps vectors of ``dim``, k kv_heads x maps, v kv_heads vectors of ``vdim``; every map is a softmax attention
+    over the same values and the head's output is a_1 - lam a_2 (one ``lam`` per layer; maps == 1: a_1), divided by its root
+    mean square over vdim (``unit_norm``) and multiplied by ``post``.  The first ``len(rates) * 2`` dimensions of every q / k
+    vector are rotated pairwise (2i with 2i+1) by position * rates[i]; score = q . k * scale; position i sees j <= i with
+    floor(i / chunk) == floor(j / chunk) (``chunk`` 0: every j <= i).  Projection columns [q | k | v]; rotated keys and the
+    values are cached per position."""
+
+    DECODE_WS_ROWS = 256
+
+    def __init__(self, width: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, eps: float, maps: int = 2,
+                 rates: Sequence[float] = (), chunk: int = 0, lam: float = 0.0, post: float = 1.0, unit_norm: bool = True):
+        if heads % kv_heads or maps not in (1, 2) or 2 * len(rates) > dim:
+            raise ValueError("heads must be a multiple of kv_heads, maps 1 or 2, and the rotated dimensions at most dim")
+        self.width, self.heads, self.kv_heads, self.dim, self.vdim, self.scale, self.eps = width, heads, kv_heads, dim, vdim, scale, eps
+        self.maps, self.rate_values, self.chunk, self.lam, self.post, self.unit_norm = maps, [float(r) for r in rates], int(chunk), lam, post, unit_norm
+        self.col_k = heads * maps * dim
+        self.col_v = self.col_k + kv_heads * maps * dim
+        self.n_proj = self.col_v + kv_heads * vdim
+        self.n_mix = heads * vdim
+        self.in_proj = Linear(width, self.n_proj)
+        self.o_proj = Linear(self.n_mix, width)
+        self.rates: Optional[torch.Tensor] = None             # fp32 on the device
+
+    def set_lambda(self, lq1, lk1, lq2, lk2, offset: float):
+        """lam = exp(lq1 . lk1) - exp(lq2 . lk2) + offset, from the layer's four vectors."""
+        f = lambda a, b: math.exp(float((a.double() * b.double()).sum()))
+        self.lam = f(lq1, lk1) - f(lq2, lk2) + float(offset)
+
+    def new_state(self, batch_size: int) -> RowState:
+        return BatchedKVCache(self.maps * self.dim, self.kv_heads, batch_size, value_dim=self.vdim)
+
+    def reserve(self, s: Scratch, dt):
+        s.reserve("proj", torch.float32, self.n_proj)
+        s.reserve("aq", torch.float32, self.col_k)
+        s.reserve("mix", dt, self.n_mix)
+        n = ops.diff_attn_workspace_floats(min(s.rows, self.DECODE_WS_ROWS), self.heads, self.maps, self.vdim)
+        if dt != torch.float32 and n:
+            s.reserve_flat("attn_ws", torch.float32, n)
+
+    def __call__(self, x, y_out, st: BatchedKVCache, plan: dict, s: Scratch, caches):
+        M, dt, f32 = x.shape[0], x.dtype, torch.float32
+        proj = self.in_proj(x, GEMM_STORE_F32, out=s.get("proj", f32, M, self.n_proj))
+        q = s.get("aq", f32, M, self.col_k)
+        ops.rope_attn_prep(proj, 0, self.col_k, self.col_v, self.rates, 2 * len(self.rate_values), self.scale, q, st.keys, st.values,
+                           plan["t_row"], plan["t_pos"], self.heads, self.kv_heads, self.maps, self.dim, self.vdim)
+        mix = s.get("mix", dt, M, self.n_mix)
+        ws = s.flat("attn_ws", f32) if (dt != f32 and ("attn_ws", f32) in s._bufs) else None
+        ops.diff_attn(q, st.keys, st.values, plan["t_row"], plan["t_pos"], mix, self.heads, self.kv_heads, self.maps, self.dim, self.vdim,
+                      chunk=self.chunk, lam=self.lam, eps=self.eps if self.unit_norm else -1.0, post=self.post, cu=plan["cu"],
+                      rows=plan["rows"], nb=plan["nb"], max_n=plan["max_n"], workspace=ws)
+        return self.o_proj(mix, GEMM_STORE_F32, out=y_out)
+
+
 class LatentAttention:
     """Attention whose queries and keys/values pass through low-rank latents; no positional rotation.
 
@@ -399,26 +538,64 @@ class ClampedGLU(GatedFF):
         super().__init__(width, ff, "clamped", limit)
 
 
+class ActivatedFF:
+    """Ungated feed-forward y = W_down act(W_up x) with the activation in the GEMM epilogue; ``act``: "relu_squared"."""
+
+    EPILOGUES = {"relu_squared": GEMM_RELU_SQ}
+
+    def __init__(self, width: int, ff: int, act: str):
+        self.width, self.ff = width, ff
+        self.epilogue = self.EPILOGUES[act]
+        self.up = Linear(width, ff)
+        self.down = Linear(ff, width)
+
+    def reserve(self, s: Scratch, dt):
+        s.reserve("act", dt, self.ff)
+
+    def __call__(self, x, y_out, s: Scratch):
+        act = self.up(x, self.epilogue, out=s.get("act", x.dtype, x.shape[0], self.ff))
+        return self.down(act, GEMM_STORE_F32, out=y_out)
+
+
 class RoutedExperts:
-    """Mixture of ``experts`` GatedFF experts of which every token uses ``top``: router logits W_r x + b in fp32, the ``top``
-    largest chosen, their weights the softmax over the chosen logits alone; y = sum of the chosen experts' weighted outputs,
-    plus a shared expert (``shared_ff`` > 0) that every token uses.  The tokens are sorted by expert on the device and every
-    expert multiplies its own contiguous rows (grouped GEMMs), so the launches do not depend on the routing."""
+    """Mixture of ``experts`` GatedFF experts of which every token uses ``top``; y = sum of the chosen experts' weighted
+    outputs, plus a shared expert (``shared_ff`` > 0) that every token uses.  Two ways to choose (``scoring``):
+      "softmax"  router logits W_r x + b in fp32, the ``top`` largest chosen, their weights the softmax over the chosen logits;
+      "sigmoid"  scores s = sigmoid(W_r x); experts are picked by s + correction (a vector per layer) among the experts of the
+                 ``groups[1]`` best of ``groups[0]`` equal groups of neighbouring experts (a group's score: the sum of its two
+                 largest picking scores); weights s / sum(chosen s) * ``route_scale``.
+    ``shared_gate``: the shared expert's output is multiplied by sigmoid(w_sg . x), one number per token (w_sg is stacked under
+    the router's rows, so the router's product yields it).
+    The tokens are sorted by expert on the device and every expert multiplies its own contiguous rows (grouped GEMMs), so the
+    launches do not depend on the routing."""
 
     def __init__(self, width: int, experts: int, top: int, ff: int, act: str, shared_ff: int = 0, shared_act: Optional[str] = None,
-                 router_bias: bool = True):
+                 router_bias: bool = True, scoring: str = "softmax", groups: Sequence[int] = (1, 1), route_scale: float = 1.0,
+                 shared_gate: bool = False):
+        if scoring not in ("softmax", "sigmoid"):
+            raise ValueError(f"unknown expert scoring {scoring!r}")
         self.width, self.experts, self.top, self.ff = width, experts, top, ff
+        self.scoring, self.groups, self.route_scale = scoring, (int(groups[0]), int(groups[1])), float(route_scale)
+        self.shared_gate = bool(shared_gate and shared_ff)
         self.epilogue = GatedFF.EPILOGUES[act]
-        self.router = Linear(width, experts)
-        self.router_bias: Optional[torch.Tensor] = None       # fp32 [experts]
+        self.n_router = _round8(experts + 1) if self.shared_gate else experts      # router rows, then the shared gate's, then zeros
+        self.router = Linear(width, self.n_router)
+        self.router_bias: Optional[torch.Tensor] = None       # fp32 [experts]: the logits' bias or the picking correction
         self.has_bias = router_bias
         self.gate_up: Optional[torch.Tensor] = None           # [experts, 2 ff, width], gate / up rows interleaved
         self.down: Optional[torch.Tensor] = None              # [experts, width, ff]
         self.shared = GatedFF(width, shared_ff, shared_act or act) if shared_ff else None
 
+    def stack_router(self, router: torch.Tensor, shared_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The router's matrix with the shared expert's gate row (and zero rows up to a multiple of 8) under it."""
+        if not self.shared_gate:
+            return router
+        pad = torch.zeros((self.n_router - self.experts - 1, router.shape[1]), dtype=router.dtype)
+        return torch.cat([router, shared_gate.reshape(1, -1).to(router.dtype), pad], 0)
+
     def reserve(self, s: Scratch, dt):
         f32, i32 = torch.float32, torch.int32
-        s.reserve("router", f32, self.experts)
+        s.reserve("router", f32, self.n_router)
         s.reserve("moe_ids", i32, self.top)
         s.reserve("moe_wts", f32, self.top)
         s.reserve("moe_slot", i32, self.top)
@@ -434,11 +611,15 @@ class RoutedExperts:
     def __call__(self, x, y_out, s: Scratch):
         M, dt, f32, i32 = x.shape[0], x.dtype, torch.float32, torch.int32
         n = M * self.top
-        logits = self.router(x, GEMM_STORE_F32, out=s.get("router", f32, M, self.experts))
+        logits = self.router(x, GEMM_STORE_F32, out=s.get("router", f32, M, self.n_router))
         ids, wts = s.get("moe_ids", i32, M, self.top), s.get("moe_wts", f32, M, self.top)
         slot_of, token_of = s.get("moe_slot", i32, M, self.top), s.get("moe_tok", i32, M, self.top)
         seg = s.flat("moe_seg", i32)
-        ops.moe_route(logits, self.router_bias, ids, wts, seg, slot_of, token_of, self.top)
+        if self.scoring == "sigmoid":
+            ops.moe_route_sigmoid(logits, self.router_bias, ids, wts, seg, slot_of, token_of, self.top, self.groups[0], self.groups[1],
+                                  self.route_scale, experts=self.experts)
+        else:
+            ops.moe_route(logits, self.router_bias, ids, wts, seg, slot_of, token_of, self.top)
         xs = s.get("moe_x", dt, n, self.width)
         ops.moe_gather(x, token_of, xs)
         act = ops.gemm_grouped(xs, self.gate_up, seg, M, self.epilogue, out=s.get("moe_act", dt, n, self.ff))
@@ -446,7 +627,7 @@ class RoutedExperts:
         ysh = None
         if self.shared is not None:
             ysh = self.shared(x, s.get("y_shared", f32, M, self.width), s)
-        ops.moe_combine(ye, slot_of, wts, ysh, y_out, self.top)
+        ops.moe_combine(ye, slot_of, wts, ysh, y_out, self.top, shared_gate=logits[:, self.experts:self.experts + 1] if self.shared_gate else None)
         return y_out
 
 
@@ -491,14 +672,17 @@ class Sublayer:
 
 
 class LayerRun:
-    """One execution of a layer of the "parallel" chain: x <- x + mixer(n(x)) + mlp(n(x)) with ONE norm n (weight ``norm_w``,
-    fp32, applied as a plain factor).  ``slot`` is the run's entry in the cache list: a layer that runs several times (a looped
-    span) has one run and one state per pass on the same modules.  ``opens``: the run is the first of a pass of the span,
-    which begins with x <- W_in [x ; embedding] (``SequenceModel.loop_in``)."""
+    """One execution of a layer of the "parallel" or the "prenorm" chain.  "parallel": x <- x + mixer(n(x)) + mlp(n(x)) with ONE
+    norm n (weight ``norm_w``, fp32, applied as a plain factor).  "prenorm": x <- x + mixer(n(x)), then x <- x + mlp(n2(x)) with a
+    second norm (``norm2_w``).  ``slot`` is the run's entry in the cache list: a layer that runs several times (a looped span)
+    has one run and one state per pass on the same modules.  ``opens``: the run is the first of a pass of the span, which
+    begins with x <- W_in [x ; embedding] (``SequenceModel.loop_in``; models without it leave every ``opens`` False)."""
 
-    def __init__(self, layer: int, slot: int, mixer, mlp, norm_w_name: str, opens: bool = False):
+    def __init__(self, layer: int, slot: int, mixer, mlp, norm_w_name: str, opens: bool = False, norm2_w_name: Optional[str] = None):
         self.layer, self.slot, self.mixer, self.mlp, self.norm_w_name, self.opens = layer, slot, mixer, mlp, norm_w_name, opens
+        self.norm2_w_name = norm2_w_name
         self.norm_w: Optional[torch.Tensor] = None
+        self.norm2_w: Optional[torch.Tensor] = None
 
 
 def unroll_layers(n_layers: int, start: int = 0, stop: int = 0, times: int = 1) -> List[tuple]:
@@ -516,7 +700,9 @@ class SequenceModel:
     plus ``forward_ragged`` for prompts of unequal length and arbitrary logit positions.  Subclasses build ``self.embed``,
     ``self.final_norm_w`` / ``self.lm_head``, name their tensors in ``load_weights``, and describe their layers in one of two
     ways: ``block_style`` "sandwich": ``self.sublayers`` (in execution order) and ``self.mixers`` (one per layer), every
-    sublayer between two norms; "parallel": ``self.runs`` (LayerRun, in execution order) and optionally ``self.loop_in``."""
+    sublayer between two norms; "parallel": ``self.runs`` (LayerRun, in execution order) and optionally ``self.loop_in``;
+    "prenorm": ``self.runs`` whose mixer and feed-forward each read a norm of their own.  ``self.logit_scale`` multiplies
+    the logits."""
 
     block_style = "sandwich"
 
@@ -541,6 +727,7 @@ class SequenceModel:
         self.final_norm_w: Optional[torch.Tensor] = None
         self.lm_head: Optional[Linear] = None
         self.eps = 1e-6
+        self.logit_scale = 1.0
         # debugging aid: callable(layer, kind, h [M, width]) run after every closed branch of an eager pass (never set it
         # while a decode step is being captured)
         self.residual_tap = None
@@ -572,7 +759,7 @@ class SequenceModel:
 
     def new_cache(self, batch_size: int) -> List[RowState]:
         """One entry per layer (its mixer's state) and a last one for the previous token of every row."""
-        if self.block_style == "parallel":
+        if self.block_style in ("parallel", "prenorm"):
             return [r.mixer.new_state(batch_size) for r in self.runs] + [TokenState(batch_size)]
         return [m.new_state(batch_size) for m in self.mixers] + [TokenState(batch_size)]
 
@@ -641,6 +828,8 @@ class SequenceModel:
         x, y = s.get("x", dt, M, W), s.get("y", torch.float32, M, W)
         if self.block_style == "parallel":
             return self._chain_parallel(h, x, y, plan, s, cache, M)
+        if self.block_style == "prenorm":
+            return self._chain_prenorm(h, x, y, plan, s, cache)
         subs = self.sublayers
 
         def feed(nxt: Optional[Sublayer], y_in, post_w):
@@ -694,6 +883,22 @@ class SequenceModel:
                 y2 = r.mlp(x, s.get("y2", torch.float32, M, W), s)
             close(i + 1, y, y2)
 
+    def _chain_prenorm(self, h, x, y, plan: dict, s: Scratch, cache: List[RowState]):
+        """The runs of a "prenorm" model over the residual stream h (fp32): x <- n1(h), h += mixer(x); x <- n2(h), h += mlp(x).
+        Every addition to the stream also writes the normed input of whatever reads it next, in the same pass over the row."""
+        dt, eps, runs = self.dtype, self.eps, self.runs
+        if runs:
+            ops.residual_add_norm(h, eps, dt, w_next=runs[0].norm_w, x_out=x)
+        for i, r in enumerate(runs):
+            nxt = runs[i + 1].norm_w if i + 1 < len(runs) else None
+            r.mixer(x, y, cache[r.slot], plan, s, cache)
+            if r.mlp is not None:
+                ops.residual_add_norm(h, eps, dt, y1=y, w_next=r.norm2_w, x_out=x)
+                r.mlp(x, y, s)
+            ops.residual_add_norm(h, eps, dt, y1=y, w_next=nxt, x_out=x if nxt is not None else None)
+            if self.residual_tap is not None:
+                self.residual_tap(r.layer, "run", h)
+
     def _advance_device(self, cache: List[RowState], a: dict, B: int, ids_i32: Optional[torch.Tensor] = None):
         """End of a step on the device: lengths += tokens brought, last token of every entry remembered."""
         ops.ragged_advance(cache[-1]._lengths, cache[-1].last_token, a["ids"] if ids_i32 is None else ids_i32, a["cu"], a["rows"], B)
@@ -703,7 +908,10 @@ class SequenceModel:
         n = h_rows.shape[0]
         xl = a["s"].get("xl", self.dtype, n, self.args.width)
         ops.norm_add_norm(h_rows, self.eps, self.dtype, w_next=self.final_norm_w, x_out=xl)
-        return self.lm_head(xl, GEMM_STORE_F32, out=logits_out)
+        logits = self.lm_head(xl, GEMM_STORE_F32, out=logits_out)
+        if self.logit_scale != 1.0:
+            ops.scale_(logits, self.logit_scale)
+        return logits
 
     def forward_ragged(self, seqs: Sequence[Sequence[int]], cache: List[RowState], rows: Optional[Sequence[int]] = None,
                        want: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:

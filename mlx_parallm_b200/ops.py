@@ -263,7 +263,7 @@ def gemm(x, w, epilogue=_lib.GEMM_STORE, out=None, limit=0.0, batch=1, strides=(
         assert w.shape[1] == K, (tuple(x.shape), tuple(w.shape))
         ldx, ldw = x.stride(0), w.stride(0)
     if out is None:
-        n_out = N // 2 if epilogue >= _lib.GEMM_GLU_CLAMP else N
+        n_out = N // 2 if _lib.gemm_is_gated(epilogue) else N
         out = torch.empty((M, n_out * batch), dtype=torch.float32 if epilogue == _lib.GEMM_STORE_F32 else x.dtype, device=x.device)
     if ldy is None:
         ldy = out.stride(0)
@@ -369,7 +369,7 @@ def gemm_grouped(x, w, seg, max_rows: int, epilogue=_lib.GEMM_STORE, out=None, l
     _dev(x, w, seg, out)
     groups, N, K = w.shape
     assert x.dtype == w.dtype and x.stride(-1) == 1 and w.is_contiguous() and x.shape[1] == K and seg.dtype == torch.int32
-    glu = epilogue >= _lib.GEMM_GLU_CLAMP
+    glu = _lib.gemm_is_gated(epilogue)
     want = torch.float32 if epilogue == _lib.GEMM_STORE_F32 else x.dtype
     if out is None:
         out = torch.empty((x.shape[0], N // 2 if glu else N), dtype=want, device=x.device)
@@ -450,11 +450,89 @@ def moe_gather(x, token_of, xs):
                                                             _stream()))
 
 
-def moe_combine(ye, slot_of, wts, shared_y, y, top: int):
-    _dev(ye, slot_of, wts, shared_y, y)
+def moe_route_sigmoid(logits, correction, ids, wts, seg, slot_of, token_of, top: int, groups: int = 1, keep: int = 1, scale: float = 1.0,
+                      experts: Optional[int] = None):
+    """Routing by sigmoid scores inside the ``keep`` best of ``groups`` expert groups; ``logits`` may hold more columns than
+    ``experts`` (say a shared expert's gate beside the router's)."""
+    _dev(logits, correction, ids, wts, seg, slot_of, token_of)
+    M = logits.shape[0]
+    E = logits.shape[1] if experts is None else int(experts)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    _call("b200p_moe_route_sigmoid", lambda: lib().b200p_moe_route_sigmoid(_p(logits), logits.stride(0), _p(correction), _p(ids), _p(wts),
+                                                                          _p(seg), _p(slot_of), _p(token_of), M, E, int(top), int(groups),
+                                                                          int(keep), float(scale), _stream()))
+
+
+def moe_combine(ye, slot_of, wts, shared_y, y, top: int, shared_gate=None):
+    """``shared_gate``: fp32 column (one pre-activation per token, any row stride) whose sigmoid multiplies ``shared_y``."""
+    _dev(ye, slot_of, wts, shared_y, y, shared_gate)
     M, W = y.shape
     assert ye.dtype == torch.float32 and ye.is_contiguous() and y.is_contiguous() and (shared_y is None or shared_y.is_contiguous())
-    _call("b200p_moe_combine", lambda: lib().b200p_moe_combine(_p(ye), _p(slot_of), _p(wts), _p(shared_y), _p(y), M, W, int(top), _stream()))
+    assert shared_gate is None or (shared_gate.dtype == torch.float32 and shared_gate.shape[0] == M)
+    _call("b200p_moe_combine", lambda: lib().b200p_moe_combine(_p(ye), _p(slot_of), _p(wts), _p(shared_y), _p(shared_gate),
+                                                              0 if shared_gate is None else shared_gate.stride(0), _p(y), M, W, int(top),
+                                                              _stream()))
+
+
+def ssm_prep(proj, col_x, col_dt, conv_w, conv_b, conv_state, A_log, dt_bias, t_row, t_pos, t_off, xs, v, kn, qn, decay, H, dv, groups,
+             state, taps):
+    """Convolution + silu of the x | B | C columns of ``proj`` (from ``col_x``), dt and the decay: the inputs of the
+    plain-accumulation scan (k = B, q = C, v = dt x) and the convolved x for the skip term."""
+    _dev(proj, conv_w, conv_b, conv_state, A_log, dt_bias, t_row, t_pos, t_off, xs, v, kn, qn, decay)
+    M = proj.shape[0]
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1
+    for t in (xs, v, kn, qn, decay):
+        assert t.dtype == torch.float32 and t.is_contiguous()
+    _call("b200p_ssm_prep", lambda: lib().b200p_ssm_prep(_p(proj), proj.stride(0), int(col_x), int(col_dt), _p(conv_w), _p(conv_b),
+                                                        _p(conv_state), _p(A_log), _p(dt_bias), _p(t_row), _p(t_pos), _p(t_off), _p(xs),
+                                                        _p(v), _p(kn), _p(qn), _p(decay), M, H, dv, groups, state, taps, _stream()))
+
+
+def ssm_out(o, xs, z, D, norm_w, out, H, dv, parts, eps):
+    """out = group_rms_norm((o + D xs) * silu(z)) * norm_w over ``parts`` equal runs of the channels; ``z`` may be a column slice."""
+    _dev(o, xs, z, D, norm_w, out)
+    M = o.shape[0]
+    assert z.dtype == torch.float32 and z.stride(1) == 1 and out.stride(1) == 1 and o.is_contiguous() and xs.is_contiguous()
+    _call("b200p_ssm_out", lambda: lib().b200p_ssm_out(_p(o), _p(xs), _p(z), z.stride(0), _p(D), _p(norm_w), _p(out), out.stride(0), M, H,
+                                                      dv, int(parts), float(eps), dtype_code(out.dtype), _stream()))
+
+
+def rope_attn_prep(proj, col_q, col_k, col_v, rates, rot_dims, scale, q_out, kcache, vcache, t_row, t_pos, H, G, maps, d, dv):
+    """Rotated, scaled queries to ``q_out`` fp32 [M, H maps d]; rotated keys and the values into the caches
+    [rows, G, Tcap, maps d] / [rows, G, Tcap, dv] at every token's (row, position)."""
+    _dev(proj, rates, q_out, kcache, vcache, t_row, t_pos)
+    M = proj.shape[0]
+    assert proj.dtype == torch.float32 and kcache.is_contiguous() and vcache.is_contiguous() and kcache.dtype == vcache.dtype
+    assert kcache.shape[1:] == (G, kcache.shape[2], maps * d) and vcache.shape[1:] == (G, kcache.shape[2], dv)
+    _call("b200p_rope_attn_prep", lambda: lib().b200p_rope_attn_prep(
+        _p(proj), proj.stride(0), int(col_q), int(col_k), int(col_v), _p(rates), int(rot_dims), float(scale), _p(q_out), _p(kcache),
+        _p(vcache), kcache.shape[2], _p(t_row), _p(t_pos), M, H, G, maps, d, dv, dtype_code(kcache.dtype), _stream()))
+
+
+def diff_attn_workspace_floats(nb: int, H: int, maps: int, dv: int) -> int:
+    return lib().b200p_diff_attn_workspace_bytes(nb, H, maps, dv) // 4
+
+
+def diff_attn(q, kcache, vcache, t_row, t_pos, out, H, G, maps, d, dv, chunk=0, lam=0.0, eps=-1.0, post=1.0, cu=None, rows=None, nb=0,
+              max_n=1, workspace=None):
+    """Chunk-masked attention with ``maps`` score maps per head over the caches: out = post * unit_rms(a_1 - lam a_2) (``eps``
+    < 0: no division by the root mean square); ``out`` [M, >= H dv] in the caches' dtype."""
+    _dev(q, kcache, vcache, t_row, t_pos, out, cu, rows, workspace)
+    M = q.shape[0]
+    assert q.dtype == torch.float32 and q.is_contiguous() and out.stride(1) == 1 and out.dtype == kcache.dtype
+    _call("b200p_diff_attn", lambda: lib().b200p_diff_attn(
+        _p(q), _p(kcache), _p(vcache), kcache.shape[2], _p(t_row), _p(t_pos), _p(cu), _p(rows), int(nb), int(max_n), int(chunk), int(maps),
+        float(lam), float(eps), float(post), _p(out), out.stride(0), M, H, G, d, dv, dtype_code(kcache.dtype), _p(workspace),
+        0 if workspace is None else workspace.numel() * 4, _stream()))
+    return out
+
+
+def scale_(y, s: float):
+    """y *= s in place (fp32, contiguous)."""
+    _dev(y)
+    assert y.dtype == torch.float32 and y.is_contiguous()
+    _call("b200p_scale", lambda: lib().b200p_scale(_p(y), y.numel(), float(s), _stream()))
+    return y
 
 
 def latent_prep(proj, q_rank, kv_rank, wq, wkv, eps, cq_out, cache, t_row, t_pos):
