@@ -343,3 +343,12 @@ def random_weights(cfg, seed=0, dtype=torch.float32):
             t = torch.randn(shape, generator=g) * 0.2
         P[name] = t.to(torch.bfloat16).to(dtype)
     return P
+
+
+def logits_error(got, want):
+    """Worst position: rms over the vocabulary of the centred difference, relative to the rms of the centred expected row."""
+    got, want = got.to(F64).cpu(), want.to(F64).cpu()
+    d = got - want
+    d = d - d.mean(-1, keepdim=True)
+    w = want - want.mean(-1, keepdim=True)
+    return float((d.pow(2).mean(-1).sqrt() / w.pow(2).mean(-1).sqrt().clamp_min(1e-30)).max())
