@@ -479,11 +479,16 @@ def _gemm_rooflines(prof, rows, w_bytes_per_el, tflops, hbm_gbs):
 def design_compare(design, sizes, steps, warmup, B_prefill=4, L_prefill=2048, B_decode=32, T_ctx=1024):
     """Prefill and decode throughput of the design at layer sizes of real models (random weights, few layers), beside the
     closest existing graph of this framework at equal width / feed-forward / head count: for Dogulorn the Llama graph (4-bit
-    weights, its usual format), for Pupopel the Dogulorn graph (dense bf16 weights, the same ragged engine)."""
+    weights, its usual format), for Pupopel the Dogulorn graph and for Nifalorn the Pupopel graph (dense bf16 weights, the same
+    ragged engine)."""
     import torch
     from mlx_parallm_b200 import _lib, ops, synth
     from mlx_parallm_b200.utils import DecodeSession, _get_classes
-    assert design in ("dogulorn", "pupopel")
+    makers = {"dogulorn": (synth.dogulorn_config, synth.dogulorn_random_weights),
+              "pupopel": (synth.pupopel_config, synth.pupopel_random_weights),
+              "nifalorn": (synth.nifalorn_config, synth.nifalorn_random_weights)}
+    closest = {"pupopel": "dogulorn", "nifalorn": "pupopel"}        # the reference graph on the same engine (Dogulorn: Llama, below)
+    assert design in makers
     _lib.require_device()
     hbm, src = peaks()
     pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
@@ -494,12 +499,8 @@ def design_compare(design, sizes, steps, warmup, B_prefill=4, L_prefill=2048, B_
         sz = DESIGN_SIZES[name]
         res = {"size": name, "dims": sz}
         # ---- the design
-        if design == "pupopel":
-            cfg = synth.pupopel_config(**sz)
-            w = synth.pupopel_random_weights(cfg, device=dev)
-        else:
-            cfg = synth.dogulorn_config(**sz)
-            w = synth.dogulorn_random_weights(cfg, device=dev)
+        cfg = makers[design][0](**sz)
+        w = makers[design][1](cfg, device=dev)
         Model, Args = _get_classes(cfg)
         model = Model(Args.from_dict(cfg)).load_weights(w, device=dev)
         del w
@@ -539,10 +540,10 @@ def design_compare(design, sizes, steps, warmup, B_prefill=4, L_prefill=2048, B_
                                                       B_decode, 2, tflops, hbm)
         del model, cache, sess
         torch.cuda.empty_cache()
-        if design == "pupopel":
-            # ---- the closest existing graph at equal size: Dogulorn (dense weights, delta rule + attention, same engine)
-            dcfg = synth.dogulorn_config(**sz)
-            dw = synth.dogulorn_random_weights(dcfg, device=dev)
+        if design in closest:
+            # ---- the closest existing graph at equal size (dense weights, recurrent layers + attention, same engine)
+            dcfg = makers[closest[design]][0](**sz)
+            dw = makers[closest[design]][1](dcfg, device=dev)
             DModel, DArgs = _get_classes(dcfg)
             dm = DModel(DArgs.from_dict(dcfg)).load_weights(dw, device=dev)
             del dw
@@ -576,7 +577,7 @@ def design_compare(design, sizes, steps, warmup, B_prefill=4, L_prefill=2048, B_
             ref["decode_launches_per_step"] = dl
             ref["decode_gemm_roofline"] = _gemm_rooflines({k: {"calls": v["calls_per_step"], "mean_us": v["mean_ms"] * 1e3} for k, v in dkp.items()},
                                                           B_decode, 2, tflops, hbm)
-            res["dogulorn_equal_size"] = ref
+            res[closest[design] + "_equal_size"] = ref
             res["prefill_kernels"] = {kk: {"calls": v["calls"], "mean_us": round(v["mean_us"], 2)} for kk, v in res["prefill_kernels"].items()}
             rows_out.append(res)
             del dm, dcache, dsess
@@ -628,7 +629,7 @@ def main():
     ap.add_argument("--sweep", default=",".join(DEFAULT_SWEEP), help="comma list of extra workloads ('' = none)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
-    ap.add_argument("--design", default=None, choices=["dogulorn", "pupopel"],
+    ap.add_argument("--design", default=None, choices=["dogulorn", "pupopel", "nifalorn"],
                     help="instead of the headline workload: prefill / decode throughput of this design at real layer sizes, "
                          "beside the closest existing graph at equal size (one JSON line of its own shape)")
     ap.add_argument("--design-sizes", default=",".join(DESIGN_SIZES))

@@ -590,8 +590,8 @@ class RoutedExperts:
         """The router's matrix with the shared expert's gate row (and zero rows up to a multiple of 8) under it."""
         if not self.shared_gate:
             return router
-        pad = torch.zeros((self.n_router - self.experts - 1, router.shape[1]), dtype=router.dtype)
-        return torch.cat([router, shared_gate.reshape(1, -1).to(router.dtype), pad], 0)
+        pad = torch.zeros((self.n_router - self.experts - 1, router.shape[1]), dtype=router.dtype, device=router.device)
+        return torch.cat([router, shared_gate.reshape(1, -1).to(device=router.device, dtype=router.dtype), pad], 0)
 
     def reserve(self, s: Scratch, dt):
         f32, i32 = torch.float32, torch.int32

@@ -402,3 +402,110 @@ def pupopel_random_weights(cfg: dict, seed: int = 1234, device="cpu", rank: Opti
             t = 1.0 + 0.02 * torch.randn(shape, generator=g, device=dev)
         out[name] = t.to(torch.bfloat16)
     return out
+
+
+# ---- Nifalorn ---------------------------------------------------------------------------------------------------------------
+def nifalorn_config(width: int, ff: int, n_layers: int, heads: int, head_dim: int, kv_heads: Optional[int] = None,
+                    ssm_head_dim: int = 64, ssm_state: int = 128, ssm_groups: int = 8, experts: int = 16, top: int = 2,
+                    expert_groups: int = 4, keep_groups: int = 2, chunk: int = 8192, vocab: int = 32000, taps: int = 4,
+                    loop_times: int = 1, **unused) -> dict:
+    """A config of the design at the sizes of a real model: layers cycle (state-space mixer of twice the width + dense
+    feed-forward, two-map attention + routed experts, constant-decay linear attention + dense); each score map has half the
+    head size, the values the whole; the routed layer's active experts and its shared expert together have the dense layer's
+    hidden size.  All layers form one span that runs ``loop_times`` times."""
+    kv_heads = kv_heads or max(1, heads // 4)
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": expert_groups, "keep": keep_groups}},
+           "expert": {"ff": ff // (2 * top)}, "shared": {"ff": ff // 2}}
+    layers = []
+    for i in range(n_layers):
+        kind = i % 3
+        if kind == 0:
+            ssm_heads = 2 * width // ssm_head_dim
+            mixer = {"heads": ssm_heads, "vdim": ssm_head_dim, "state": ssm_state, "groups": ssm_groups, "norm_groups": ssm_groups, "conv": taps}
+            layers.append({"type": "mamba2", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}})
+        elif kind == 1:
+            mixer = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim // 2, "vdim": head_dim, "scale": (head_dim // 2) ** -0.5, "diff": 0.6,
+                     "mask": {"size": chunk},
+                     "rot": {"dims": head_dim // 2, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+            layers.append({"type": "attention", "mixer": mixer, "mlp": moe})
+        else:
+            mixer = {"heads": heads, "dim": head_dim, "vdim": head_dim,
+                     "decay": [1.0 - 2.0 ** (-4.0 - 6.0 * h / max(1, heads - 1)) for h in range(heads)]}
+            layers.append({"type": "lightning", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}})
+    return {"architecture": "Nifalorn", "vocab": vocab, "width": width, "layers": layers, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "logit_scale": 1.0, "loop": {"start": 0, "stop": n_layers, "times": loop_times}}
+
+
+def nifalorn_shapes(cfg: dict) -> Dict[str, tuple]:
+    """Shape of every tensor of a Nifalorn checkpoint (matrices [out, in])."""
+    W, V = cfg["width"], cfg["vocab"]
+    out = {"embed": (V, W), "head": (V, W), "final.norm": (W,)}
+
+    def glu(p, ff):
+        out[p + "gate"] = out[p + "up"] = (ff, W)
+        out[p + "down"] = (W, ff)
+
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.mix.", L["mixer"]
+        out[f"l{i}.norm1"] = (W,)
+        if L["type"] == "mamba2":
+            inner, gn = m["heads"] * m["vdim"], m["groups"] * m["state"]
+            out[p + "in"] = (2 * inner + 2 * gn + m["heads"], W)
+            out[p + "conv"], out[p + "conv.b"] = (inner + 2 * gn, m.get("conv", 1)), (inner + 2 * gn,)
+            out[p + "dt_bias"] = out[p + "A_log"] = out[p + "D"] = (m["heads"],)
+            out[p + "norm"], out[p + "o"] = (inner,), (W, inner)
+        elif L["type"] == "attention":
+            G = m.get("kv_heads", m["heads"])
+            out[p + "q"], out[p + "k"], out[p + "v"] = (m["heads"] * 2 * m["dim"], W), (G * 2 * m["dim"], W), (G * m["vdim"], W)
+            for n in ("lq1", "lk1", "lq2", "lk2"):
+                out[p + n] = (m["dim"],)
+            out[p + "o"] = (W, m["heads"] * m["vdim"])
+        else:
+            cq, cv = m["heads"] * m["dim"], m["heads"] * m["vdim"]
+            out[p + "q"] = out[p + "k"] = (cq, W)
+            out[p + "v"] = out[p + "g"] = (cv, W)
+            out[p + "norm"], out[p + "o"] = (cv,), (W, cv)
+        mlp = L.get("mlp")
+        if mlp is None:
+            continue
+        q = f"l{i}.mlp."
+        out[f"l{i}.norm2"] = (W,)
+        if mlp["kind"] == "dense":
+            out[q + "up"], out[q + "down"] = (mlp["ff"], W), (W, mlp["ff"])
+        else:
+            for e in range(mlp["router"]["experts"]):
+                glu(f"{q}e{e}.", mlp["expert"]["ff"])
+            out[q + "router"], out[q + "correction"] = (mlp["router"]["experts"], W), (mlp["router"]["experts"],)
+            if (mlp.get("shared") or {}).get("ff"):
+                glu(q + "shared.", mlp["shared"]["ff"])
+                out[q + "shared.sg"] = (1, W)
+    return out
+
+
+def nifalorn_random_weights(cfg: dict, seed: int = 1234, device="cpu") -> Dict[str, torch.Tensor]:
+    """bfloat16 tensors: matrices N(0, 1/in), norm offsets N(0, 0.02) (weights that multiply directly: 1 + that), convolution
+    taps N(0, 0.25), decay parameters spread so that heads forget at different speeds, small picking corrections."""
+    dev = torch.device(device)
+    out: Dict[str, torch.Tensor] = {}
+    for name, shape in nifalorn_shapes(cfg).items():
+        g = torch.Generator(device=dev)
+        g.manual_seed(_stable_seed(seed, name))
+        leaf = name.rsplit(".", 1)[-1]
+        if len(shape) == 2 and leaf != "conv":
+            t = torch.randn(shape, generator=g, device=dev) / math.sqrt(shape[1])
+            if name == "embed":
+                t = t * math.sqrt(shape[1]) * 0.5
+        elif leaf == "conv":
+            t = torch.randn(shape, generator=g, device=dev) * 0.5
+        elif leaf == "A_log":
+            t = torch.rand(shape, generator=g, device=dev) * 3.0 - 2.0
+        elif leaf == "dt_bias":
+            t = torch.randn(shape, generator=g, device=dev) - 1.0
+        elif leaf in ("correction", "b", "lq1", "lk1", "lq2", "lk2"):
+            t = 0.1 * torch.randn(shape, generator=g, device=dev)
+        elif leaf in ("norm1", "norm2") or name == "final.norm":
+            t = 0.02 * torch.randn(shape, generator=g, device=dev)
+        else:                                   # mix.norm, D
+            t = 1.0 + 0.02 * torch.randn(shape, generator=g, device=dev)
+        out[name] = t.to(torch.bfloat16)
+    return out
