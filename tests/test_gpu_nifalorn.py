@@ -317,7 +317,7 @@ def test_attention_far_keys_and_chunk_borders(T, chunk, hq, hk, visible, decode)
 def test_attention_tile_sizes_far_keys_and_tile_borders(T, chunk, hq, hk):
     """Sizes the tensor-core kernel takes (16-bit, vector and value sizes 32, 64, 128): hot pairs across its key tiles and its
     query tiles, chunks that start inside a tile, prompts and single tokens."""
-    for d, dv in ((64, 64), (128, 64), (64, 128), (32, 32), (32, 128)):
+    for d, dv in ((64, 64), (128, 64), (64, 128), (32, 32), (32, 128), (128, 128), (32, 64), (64, 32), (128, 32)):
         for decode in (False, True):
             if decode and T > 200:
                 continue
