@@ -68,7 +68,7 @@ def test_config_checks():
         Args.from_dict(dict(cfg, layers=[O.lightning_layer(1, 8, 8, [0.5], mlp=O.moe_mlp(6, 5, 8, groups=(3, 2)))]))
 
 
-@pytest.mark.parametrize("dims,base,scaling", [(8, 10000.0, None), (16, 1e6, (4.0, 1.0, 4.0, 1024)), (32, 500000.0, (8.0, 1.0, 4.0, 8192)),
+@pytest.mark.parametrize("dims,base,scaling", [(8, 10000.0, None), (16, 5e5, (4.0, 1.0, 8.0, 2048)), (32, 500000.0, (8.0, 1.0, 4.0, 8192)),
                                                 (6, 100.0, (2.0, 1.0, 8.0, 64))])
 def test_rotation_rates(dims, base, scaling):
     from mlx_parallm_b200.models._sequence import rotary_rates
