@@ -402,7 +402,14 @@ int b200p_moe_gather(const void* x, const int32_t* token_of, void* xs, int64_t s
 int b200p_moe_route_sigmoid(const float* logits, int64_t ldl, const float* correction, int32_t* ids, float* wts, int32_t* seg,
                             int32_t* slot_of, int32_t* token_of, int64_t M, int E, int top, int count, int keep, float scale,
                             void* stream);
-/* y[t, :] = (shared_y ? g[t] * shared_y[t, :] : 0) + sum_k wts[t, k] * ye[slot_of[t, k], :], all fp32;
+/* The same outputs from plain sigmoid scores: the `top` largest s = sigmoid(logits) are picked (ties to the smaller index) and
+ * wts are those scores as they are, not renormalised. */
+int b200p_moe_route_scores(const float* logits, int64_t ldl, int32_t* ids, float* wts, int32_t* seg, int32_t* slot_of,
+                           int32_t* token_of, int64_t M, int E, int top, void* stream);
+/* xs[slot_of[t, k], :] = wts[t, k] * x[t, :] (fp32 product rounded to `dtype`): routing weights that multiply the experts' inputs */
+int b200p_moe_scatter_scaled(const void* x, const int32_t* slot_of, const float* wts, void* xs, int64_t M, int64_t W, int top,
+                             int dtype, void* stream);
+/* y[t, :] = (shared_y ? g[t] * shared_y[t, :] : 0) + sum_k wts[t, k] * ye[slot_of[t, k], :], all fp32 (wts NULL: weights of one);
  * g[t] = sigmoid(shared_gate[t * ldg]) (shared_gate NULL: 1) */
 int b200p_moe_combine(const float* ye, const int32_t* slot_of, const float* wts, const float* shared_y, const float* shared_gate,
                       int64_t ldg, float* y, int64_t M, int64_t W, int top, void* stream);
@@ -470,6 +477,58 @@ int b200p_latent_attn_set_buffers(int buffers);
 int b200p_latent_attn_tiles(const float* q, const void* cache, int64_t Tcap, const int32_t* cu, const int32_t* rows,
                             const int32_t* t_pos, void* out, int nb, int max_n, int H, int R, int64_t window, float scale,
                             int dtype, void* stream);
+
+
+/* Latent attention whose keys also have a rotated part shared by all heads.  Step 1 as b200p_latent_prep with
+ * proj = [query (q_rank) | key/value (kv_rank) | rotated key part (rot_dim)]; the cache row ([rows, Tcap, row], row >= kv_rank +
+ * rot_dim) becomes [rms-normed latent * wkv | rotated part | zeros]: the pairs (2i, 2i+1) of the rotated part turn by the angle
+ * position * rates[i] (fp32) and are multiplied by mag. */
+int b200p_latent_rope_prep(const float* proj, int64_t ldp, int q_rank, int kv_rank, int rot_dim, int row, const float* wq,
+                           const float* wkv, float eps, const float* rates, float mag, void* cq_out, void* cache, int64_t Tcap,
+                           const int32_t* t_row, const int32_t* t_pos, int64_t M, int dtype, void* stream);
+/* The queries' rotated part: q [M, H, dim + rot_dim] (dtype); the last rot_dim values of every head turn like the keys' and go,
+ * fp32, to q_lat [M, H, row] columns [kv_rank, kv_rank + rot_dim); the columns behind them become zero.  (The columns before
+ * them are the query carried into the latent space by a product of the caller's.)  b200p_latent_attn over rows of `row`
+ * values then scores q_lat . cache row = unrotated part + rotated part. */
+int b200p_latent_q_rope(const void* q, int H, int dim, int rot_dim, int kv_rank, int row, const float* rates, float mag,
+                        const int32_t* t_pos, float* q_lat, int64_t M, int dtype, void* stream);
+
+/* Windowed attention with capped scores for designs without rotation.  Step 1: proj fp32 [M, ldp] holds q (H x dk) | k (G x dk)
+ * from column col_q; both pass a causal convolution over time (conv_w [(H + G) dk, taps], the last tap the current token's;
+ * conv_state [rows, taps-1, (H + G) dk] carries the inputs of earlier steps: commit it afterwards with b200p_delta_conv_commit on the
+ * same columns; taps == 1: one factor per channel).  q_out fp32 [M, H dk] = that * scale; the keys go to kcache [rows, G, Tcap, dk]. */
+int b200p_window_attn_prep(const float* proj, int64_t ldp, int64_t col_q, const float* conv_w, const float* conv_state, int taps,
+                           float scale, float* q_out, void* kcache, int64_t Tcap, const int32_t* t_row, const int32_t* t_pos,
+                           const int32_t* t_off, int64_t M, int H, int G, int dk, int dtype, void* stream);
+/* Step 2: score s = q . k; softcap > 0: s <- softcap tanh(s / softcap); r1, r2 (fp32 [H], or both NULL): s <- s - r1[h] ln(1 +
+ * r2[h] (p - j)); the token at position p sees j with 0 <= p - j < window (window 0: every j <= p); fp32 softmax; out[t, h, :]
+ * (dtype, row stride ld_out) = sum_j p_j v_j * sigmoid(gate[t * ldg + h dv + c]) (gate fp32, NULL: no gate).  vcache may be kcache
+ * (values that are the keys).  The ragged description, the workspace and the choice of kernels are b200p_sink_attn's; the
+ * tensor-core tiles take dk == dv of 64 or 128. */
+int b200p_window_attn(const float* q, const void* kcache, const void* vcache, int64_t Tcap, const int32_t* t_row,
+                      const int32_t* t_pos, const int32_t* cu, const int32_t* rows, int nb, int max_n, float softcap,
+                      const float* r1, const float* r2, int64_t window, const float* gate, int64_t ldg, void* out, int64_t ld_out,
+                      int64_t M, int H, int G, int dk, int dv, int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Several copies of the residual stream.  xs fp32 [M, streams, W].  One pass over a token closes a sublayer and opens the next:
+ *   x'_r = sum_s mix[s, r] x_s + out[r] y   (mix [streams, streams] indexed [from, to], out [streams]; both NULL: x' = x;
+ *                                            src [M, W] given: every old copy is src, the start of a model)
+ *   sum_out [M, W] (or NULL) = sum_r x'_r
+ *   u = sum_r in[r] x'_r;  n = tanh(alpha[0] u) w + b  (w NULL: n = u; b NULL: no offset);  n_out [M, W] (or NULL) = n
+ * With x_out (dtype [M, W]) the step is a decode step, one token per entry, and the pass also adds the causal convolution over time
+ * of n: x = n + sum_j conv_w[:, j] n_(t - taps + 1 + j) from conv_state [rows, taps-1, W] (inputs before position 0 count as zero),
+ * then shifts n into conv_state.  streams <= 8, taps <= 16. */
+int b200p_hyper_step(float* xs, const float* y, const float* src, const float* mix, const float* out, const float* in,
+                     const float* alpha, const float* w, const float* b, float* n_out, float* sum_out, int64_t M, int streams,
+                     int64_t W, const float* conv_w, float* conv_state, const int32_t* t_row, const int32_t* t_pos, int taps,
+                     void* x_out, int dtype, void* stream);
+/* The same convolution for steps of several tokens per entry: x_out (dtype) = n + conv(n) over the portion's rows of n [M, W] and,
+ * before the portion, conv_state (commit it afterwards with b200p_delta_conv_commit on n). */
+int b200p_canon_conv(const float* n, const float* conv_w, const float* conv_state, const int32_t* t_row, const int32_t* t_pos,
+                     const int32_t* t_off, void* x_out, int64_t M, int64_t W, int taps, int dtype, void* stream);
+/* x_out (dtype [M, W]) = tanh(alpha[0] h) w + b: the norm without statistics, on given rows */
+int b200p_tanh_norm(const float* h, const float* alpha, const float* w, const float* b, void* x_out, int64_t M, int64_t W,
+                    int dtype, void* stream);
 
 #ifdef __cplusplus
 }

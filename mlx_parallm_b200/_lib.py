@@ -91,6 +91,8 @@ SIGNATURES = {
     "b200p_moe_gather": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp]),
     "b200p_moe_route_sigmoid": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f32, _vp]),
     "b200p_moe_combine": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i32, _vp]),
+    "b200p_moe_route_scores": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp]),
+    "b200p_moe_scatter_scaled": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp]),
     "b200p_ssm_prep": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32,
                               _i32, _i32, _i32, _vp]),
     "b200p_ssm_out": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _f32, _i32, _vp]),
@@ -107,6 +109,17 @@ SIGNATURES = {
     "b200p_latent_attn_set_buffers": (_i32, [_i32]),
     "b200p_latent_attn_tiles_supported": (_i32, [_i32, _i32]),
     "b200p_latent_attn_tiles": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i64, _f32, _i32, _vp]),
+    "b200p_latent_rope_prep": (_i32, [_vp, _i64, _i32, _i32, _i32, _i32, _vp, _vp, _f32, _vp, _f32, _vp, _vp, _i64, _vp, _vp, _i64, _i32,
+                                      _vp]),
+    "b200p_latent_q_rope": (_i32, [_vp, _i32, _i32, _i32, _i32, _i32, _vp, _f32, _vp, _vp, _i64, _i32, _vp]),
+    "b200p_window_attn_prep": (_i32, [_vp, _i64, _i64, _vp, _vp, _i32, _f32, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32,
+                                      _vp]),
+    "b200p_window_attn": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i32, _i32, _f32, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64,
+                                 _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
+    "b200p_hyper_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i64, _vp, _vp, _vp, _vp, _i32, _vp,
+                                _i32, _vp]),
+    "b200p_canon_conv": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp]),
+    "b200p_tanh_norm": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _vp]),
 }
 
 # Translation units a model family needs (csrc/*.cu): the library can be linked from a subset, so that a fresh checkout
@@ -115,6 +128,8 @@ UNIT_SETS = {
     "sequence": ("runtime", "dense_gemm", "dense_gemm_tc", "ragged", "delta_rule", "latent_attn", "sampler"),
     "sequence_moe": ("runtime", "dense_gemm", "dense_gemm_tc", "ragged", "delta_rule", "sink_attn", "moe", "sampler"),
     "sequence_ssm": ("runtime", "dense_gemm", "dense_gemm_tc", "ragged", "delta_rule", "ssm", "diff_attn", "moe", "sampler"),
+    "sequence_hyper": ("runtime", "dense_gemm", "dense_gemm_tc", "ragged", "hyper", "delta_rule", "latent_attn", "sink_attn", "moe",
+                       "sampler"),
 }
 GEMM_STORE, GEMM_STORE_F32, GEMM_GLU_CLAMP, GEMM_GLU_GELU_TANH, GEMM_GLU_SILU, GEMM_RELU_SQ = 0, 1, 2, 3, 4, 5
 

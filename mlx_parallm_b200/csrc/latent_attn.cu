@@ -41,6 +41,71 @@ __global__ void latent_prep_kernel(const float* __restrict__ proj, int64_t ldp, 
   }
 }
 
+// The same two norms for designs whose keys also have a rotated part that all heads share: proj = [query (q_rank) | key/value
+// (kv_rank) | rotated key part (rot_dim)].  The cache row is [normed latent | rotated part | zeros up to `row`]: the pairs
+// (2i, 2i+1) of the last part turn by the angle position * rates[i] (fp32, accurate sine and cosine) and are multiplied by `mag`.
+template <typename T>
+__global__ void latent_rope_prep_kernel(const float* __restrict__ proj, int64_t ldp, int q_rank, int kv_rank, int rot_dim, int row,
+                                        const float* __restrict__ wq, const float* __restrict__ wkv, float eps,
+                                        const float* __restrict__ rates, float mag, T* __restrict__ cq_out, T* __restrict__ cache,
+                                        int64_t Tcap, const int32_t* __restrict__ t_row, const int32_t* __restrict__ t_pos) {
+  const int64_t t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;     // warp 0: query part, warp 1: key/value part, warp 2: rotated part
+  const int64_t pos = t_pos[t];
+  T* dst = cache + ((int64_t)t_row[t] * Tcap + pos) * row;
+  if (warp == 2) {
+    if (pos >= Tcap) return;                                       // the host sizes the cache first; never write outside it
+    const float* src = proj + t * ldp + q_rank + kv_rank;
+    for (int i = lane; i < rot_dim / 2; i += 32) {
+      float sn, cs;
+      sincosf((float)pos * rates[i], &sn, &cs);
+      sn *= mag; cs *= mag;
+      const float u = src[2 * i], v = src[2 * i + 1];
+      dst[kv_rank + 2 * i] = Tr<T>::from_f(u * cs - v * sn);
+      dst[kv_rank + 2 * i + 1] = Tr<T>::from_f(v * cs + u * sn);
+    }
+    for (int i = kv_rank + rot_dim + lane; i < row; i += 32) dst[i] = Tr<T>::from_f(0.f);
+    return;
+  }
+  const float* src = proj + t * ldp + (warp == 0 ? 0 : q_rank);
+  const int n = warp == 0 ? q_rank : kv_rank;
+  float ss = 0.f;
+  for (int i = lane; i < n; i += 32) ss = fmaf(src[i], src[i], ss);
+  ss = warp_sum(ss);
+  const float inv = 1.f / sqrtf(ss / (float)n + eps);
+  if (warp == 0) {
+    for (int i = lane; i < n; i += 32) cq_out[t * q_rank + i] = Tr<T>::from_f(src[i] * inv * wq[i]);
+  } else {
+    if (pos >= Tcap) return;
+    for (int i = lane; i < n; i += 32) dst[i] = Tr<T>::from_f(src[i] * inv * wkv[i]);
+  }
+}
+
+// The rotated part of the queries, q [M, H, dim + rot_dim] in the storage type: its last rot_dim values turn like the keys' and
+// go, fp32, behind the latent-space part of the head's query row, q_lat [M, H, row] columns [kv_rank, kv_rank + rot_dim); the
+// columns up to `row` become zero.
+template <typename T>
+__global__ void latent_q_rope_kernel(const T* __restrict__ q, int H, int dim, int rot_dim, int kv_rank, int row,
+                                     const float* __restrict__ rates, float mag, const int32_t* __restrict__ t_pos,
+                                     float* __restrict__ q_lat) {
+  const int64_t t = blockIdx.x;
+  const float pos = (float)t_pos[t];
+  const int half = rot_dim / 2, tail = row - kv_rank - rot_dim;
+  for (int idx = threadIdx.x; idx < H * half; idx += blockDim.x) {
+    const int h = idx / half, i = idx % half;
+    float sn, cs;
+    sincosf(pos * rates[i], &sn, &cs);
+    sn *= mag; cs *= mag;
+    const T* src = q + (t * H + h) * (int64_t)(dim + rot_dim) + dim;
+    const float u = Tr<T>::to_f(src[2 * i]), v = Tr<T>::to_f(src[2 * i + 1]);
+    float* dst = q_lat + (t * H + h) * (int64_t)row + kv_rank;
+    dst[2 * i] = u * cs - v * sn;
+    dst[2 * i + 1] = v * cs + u * sn;
+  }
+  for (int idx = threadIdx.x; idx < H * tail; idx += blockDim.x)
+    q_lat[(t * H + idx / tail) * (int64_t)row + kv_rank + rot_dim + idx % tail] = 0.f;
+}
+
 constexpr int LA_KEYS = 32;       // keys per staged chunk: one per lane in the score phase
 constexpr int LA_MAX_HEADS = 8;   // heads (warps) per CTA
 constexpr int LA_MAX_RL = 32;     // latent elements per lane in the output phase: R <= 1024
@@ -353,6 +418,31 @@ extern "C" int b200p_latent_prep(const float* proj, int64_t ldp, int q_rank, int
   B200P_DISPATCH_DTYPE(dtype, T, (latent_prep_kernel<T><<<(unsigned)M, 64, 0, (cudaStream_t)stream>>>(
       proj, ldp, q_rank, kv_rank, wq, wkv, eps, (T*)cq_out, (T*)cache, Tcap, t_row, t_pos)));
   B200P_LAUNCH_CHECK("latent_prep_kernel");
+  return B200P_OK;
+}
+
+extern "C" int b200p_latent_rope_prep(const float* proj, int64_t ldp, int q_rank, int kv_rank, int rot_dim, int row, const float* wq,
+                                      const float* wkv, float eps, const float* rates, float mag, void* cq_out, void* cache,
+                                      int64_t Tcap, const int32_t* t_row, const int32_t* t_pos, int64_t M, int dtype, void* stream) {
+  B200P_REQUIRE(proj && wq && wkv && cq_out && cache && t_row && t_pos, B200P_ERR_ARG, "null pointer");
+  B200P_REQUIRE(q_rank > 0 && kv_rank > 0 && rot_dim >= 0 && rot_dim % 2 == 0 && row >= kv_rank + rot_dim && Tcap > 0, B200P_ERR_ARG,
+                "bad ranks: an even rotated part and a cache row that holds latent and rotated part");
+  B200P_REQUIRE(rot_dim == 0 || rates, B200P_ERR_ARG, "the rotated part needs its rates");
+  if (M == 0) return B200P_OK;
+  B200P_DISPATCH_DTYPE(dtype, T, (latent_rope_prep_kernel<T><<<(unsigned)M, 96, 0, (cudaStream_t)stream>>>(
+      proj, ldp, q_rank, kv_rank, rot_dim, row, wq, wkv, eps, rates, mag, (T*)cq_out, (T*)cache, Tcap, t_row, t_pos)));
+  B200P_LAUNCH_CHECK("latent_rope_prep_kernel");
+  return B200P_OK;
+}
+
+extern "C" int b200p_latent_q_rope(const void* q, int H, int dim, int rot_dim, int kv_rank, int row, const float* rates, float mag,
+                                   const int32_t* t_pos, float* q_lat, int64_t M, int dtype, void* stream) {
+  B200P_REQUIRE(q && t_pos && q_lat && (rot_dim == 0 || rates), B200P_ERR_ARG, "null pointer");
+  B200P_REQUIRE(H > 0 && dim >= 0 && rot_dim >= 0 && rot_dim % 2 == 0 && row >= kv_rank + rot_dim, B200P_ERR_ARG, "bad sizes");
+  if (M == 0 || row == kv_rank) return B200P_OK;
+  B200P_DISPATCH_DTYPE(dtype, T, (latent_q_rope_kernel<T><<<(unsigned)M, 128, 0, (cudaStream_t)stream>>>(
+      (const T*)q, H, dim, rot_dim, kv_rank, row, rates, mag, t_pos, q_lat)));
+  B200P_LAUNCH_CHECK("latent_q_rope_kernel");
   return B200P_OK;
 }
 

@@ -59,7 +59,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ldl, 
 // largest picking scores win, ties to the smaller index; weights w_k = s_k / (sum of the picked s + 1e-20) * scale.
 __global__ void moe_route_sigmoid_kernel(const float* __restrict__ logits, int64_t ldl, const float* __restrict__ correction,
                                          int32_t* __restrict__ ids, float* __restrict__ wts, int64_t M, int E, int top, int count,
-                                         int keep, float scale) {
+                                         int keep, float scale, int renorm) {
   extern __shared__ float mr_sm[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
@@ -127,7 +127,7 @@ __global__ void moe_route_sigmoid_kernel(const float* __restrict__ logits, int64
   }
   if (lane < top) {
     ids[t * top + lane] = my_id;
-    wts[t * top + lane] = mine / (den + 1e-20f) * scale;
+    wts[t * top + lane] = renorm ? mine / (den + 1e-20f) * scale : mine * scale;       // renorm 0: the scores as they are
   }
 }
 
@@ -169,6 +169,20 @@ __global__ void moe_gather_kernel(const T* __restrict__ x, const int32_t* __rest
   }
 }
 
+// xs[slot_of[t, k], :] = wts[t, k] * x[t, :]: designs whose routing weight multiplies the expert's INPUT (the product is
+// formed in fp32 and rounded once to the storage type)
+template <typename T>
+__global__ void moe_scatter_scaled_kernel(const T* __restrict__ x, const int32_t* __restrict__ slot_of, const float* __restrict__ wts,
+                                          T* __restrict__ xs, int64_t W) {
+  const int64_t i = blockIdx.x;                        // (token, choice)
+  const int top = gridDim.y;
+  const int64_t tk = i * top + blockIdx.y;
+  const float w = wts[tk];
+  const T* src = x + i * W;
+  T* dst = xs + (int64_t)slot_of[tk] * W;
+  for (int64_t c = threadIdx.x; c < W; c += blockDim.x) dst[c] = Tr<T>::from_f(w * Tr<T>::to_f(src[c]));
+}
+
 __global__ void moe_combine_kernel(const float* __restrict__ ye, const int32_t* __restrict__ slot_of, const float* __restrict__ wts,
                                    const float* __restrict__ shared_y, const float* __restrict__ shared_gate, int64_t ldg,
                                    float* __restrict__ y, int64_t W, int top) {
@@ -178,7 +192,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ ye, const int32_t* 
   __shared__ float wt[MOE_MAX_TOP];
   if (threadIdx.x < top) {
     sl[threadIdx.x] = slot_of[t * top + threadIdx.x];
-    wt[threadIdx.x] = wts[t * top + threadIdx.x];
+    wt[threadIdx.x] = wts ? wts[t * top + threadIdx.x] : 1.f;
   }
   __syncthreads();
   for (int64_t c = threadIdx.x; c < W; c += blockDim.x) {
@@ -224,10 +238,41 @@ extern "C" int b200p_moe_route_sigmoid(const float* logits, int64_t ldl, const f
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(moe_route_sigmoid_kernel)");
   }
   moe_route_sigmoid_kernel<<<(unsigned)((M + warps - 1) / warps), warps * 32, smem, st>>>(logits, ldl, correction, ids, wts, M, E, top,
-                                                                                           count, keep, scale);
+                                                                                           count, keep, scale, 1);
   B200P_LAUNCH_CHECK("moe_route_sigmoid_kernel");
   moe_plan_kernel<<<1, 1024, 2 * E * sizeof(int32_t), st>>>(ids, seg, slot_of, token_of, M * top, E, top);
   B200P_LAUNCH_CHECK("moe_plan_kernel");
+  return B200P_OK;
+}
+
+extern "C" int b200p_moe_route_scores(const float* logits, int64_t ldl, int32_t* ids, float* wts, int32_t* seg, int32_t* slot_of,
+                                      int32_t* token_of, int64_t M, int E, int top, void* stream) {
+  B200P_REQUIRE(logits && ids && wts && seg && slot_of && token_of, B200P_ERR_ARG, "null pointer");
+  B200P_REQUIRE(E > 0 && E <= 32 * MOE_MAX_PER_LANE && top > 0 && top <= E && top <= MOE_MAX_TOP, B200P_ERR_ARG,
+                "experts in [1, %d] and top in [1, min(experts, %d)]", 32 * MOE_MAX_PER_LANE, MOE_MAX_TOP);
+  if (M == 0) return B200P_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int warps = 4;
+  const size_t smem = (size_t)warps * (2 * E + 1) * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(moe_route_sigmoid_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(moe_route_sigmoid_kernel)");
+  }
+  moe_route_sigmoid_kernel<<<(unsigned)((M + warps - 1) / warps), warps * 32, smem, st>>>(logits, ldl, nullptr, ids, wts, M, E, top, 1, 1,
+                                                                                           1.f, 0);
+  B200P_LAUNCH_CHECK("moe_route_sigmoid_kernel");
+  moe_plan_kernel<<<1, 1024, 2 * E * sizeof(int32_t), st>>>(ids, seg, slot_of, token_of, M * top, E, top);
+  B200P_LAUNCH_CHECK("moe_plan_kernel");
+  return B200P_OK;
+}
+
+extern "C" int b200p_moe_scatter_scaled(const void* x, const int32_t* slot_of, const float* wts, void* xs, int64_t M, int64_t W, int top,
+                                        int dtype, void* stream) {
+  B200P_REQUIRE(x && slot_of && wts && xs && W > 0 && top > 0 && top <= MOE_MAX_TOP, B200P_ERR_ARG, "null pointer or bad top");
+  if (M == 0) return B200P_OK;
+  B200P_DISPATCH_DTYPE(dtype, T, (moe_scatter_scaled_kernel<T><<<dim3((unsigned)M, (unsigned)top), 128, 0, (cudaStream_t)stream>>>(
+      (const T*)x, slot_of, wts, (T*)xs, W)));
+  B200P_LAUNCH_CHECK("moe_scatter_scaled_kernel");
   return B200P_OK;
 }
 
@@ -242,7 +287,7 @@ extern "C" int b200p_moe_gather(const void* x, const int32_t* token_of, void* xs
 
 extern "C" int b200p_moe_combine(const float* ye, const int32_t* slot_of, const float* wts, const float* shared_y,
                                  const float* shared_gate, int64_t ldg, float* y, int64_t M, int64_t W, int top, void* stream) {
-  B200P_REQUIRE(ye && slot_of && wts && y && W > 0 && top > 0 && top <= MOE_MAX_TOP, B200P_ERR_ARG, "null pointer or bad top");
+  B200P_REQUIRE(ye && slot_of && y && W > 0 && top > 0 && top <= MOE_MAX_TOP, B200P_ERR_ARG, "null pointer or bad top");
   if (M == 0) return B200P_OK;
   moe_combine_kernel<<<(unsigned)M, W >= 1024 ? 256 : 128, 0, (cudaStream_t)stream>>>(ye, slot_of, wts, shared_y, shared_gate, ldg, y, W, top);
   B200P_LAUNCH_CHECK("moe_combine_kernel");

@@ -10,10 +10,32 @@
 // The softmax starts from the sink: running maximum = sink, running sum = 1 (the sink's own term), accumulator = 0; every key
 // then joins by the usual online update, so a query that sees few keys is damped exactly as the definition says.
 // Every option is a parameter: no norm (weights NULL), no temperature (coef 0), no bias (slope_log2 0), no sink (NULL).
+// A second family of options (ScoreRule; b200p_window_attn) serves designs that cap their scores, cap tanh(s / cap), take a
+// logarithmic distance penalty r1_h ln(1 + r2_h (i - j)) off them, see a sliding window 0 <= i - j < window, and gate the
+// heads' outputs with a sigmoid:
+//   window_attn_prep_kernel  a short causal convolution over time on the q and k projections (carried inputs like the delta
+//                            rule's), q scaled into fp32, k into the cache                                          (per token)
 #include "common.cuh"
 #include "mma_util.cuh"
 
 namespace b200p {
+
+// What happens to a score s = q . k (q already scaled) of the query at position p and the key at position j, and to the output.
+struct ScoreRule {
+  float cap;            // > 0: s <- cap tanh(s / cap)
+  const float* r1;      // per head: s <- s - r1[h] ln(1 + r2[h] (p - j)); NULL: none
+  const float* r2;
+  int window;           // > 0: only keys with 0 <= p - j < window are seen
+  const float* gate;    // fp32 [M, ldg]: out[t, h, c] *= sigmoid(gate[t, h dv + c]); NULL: none
+  int64_t ldg;
+};
+
+__device__ __forceinline__ float ruled_score(float s, const ScoreRule& rule, float r1, float r2, float dist) {
+  if (rule.cap > 0.f) s = rule.cap * tanhf(s / rule.cap);
+  if (rule.r1) s -= r1 * log1pf(r2 * dist);
+  return s;
+}
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
 
 // slope of head h: 2^(slope_log2 * (h + 1) / H); slope_log2 = 0 means no bias
 __device__ __forceinline__ float head_slope(float slope_log2, int h, int H) {
@@ -70,7 +92,8 @@ template <typename T>
 __global__ void __launch_bounds__(SA_MAX_HEADS * 32)
 sink_attn_kernel(const float* __restrict__ q, const T* __restrict__ kcache, const T* __restrict__ vcache, int64_t Tcap,
                  const int32_t* __restrict__ t_row, const int32_t* __restrict__ t_pos, const float* __restrict__ sink,
-                 float slope_log2, T* __restrict__ out, int64_t ld_out, float out_scale, int H, int G, int dk, int dv) {
+                 float slope_log2, T* __restrict__ out, int64_t ld_out, float out_scale, int H, int G, int dk, int dv,
+                 ScoreRule rule) {
   extern __shared__ float sa_sm[];
   const int KS = dk + 1;                                           // padded row: lane j reads row j without bank conflicts
   float* ks = sa_sm;                                               // [SA_KEYS][KS]
@@ -93,7 +116,9 @@ sink_attn_kernel(const float* __restrict__ q, const T* __restrict__ kcache, cons
   for (int i = 0; i < SA_MAX_VL; ++i) acc[i] = 0.f;
   float mx = (head_ok && sink) ? sink[h] : -INFINITY;
   float den = (head_ok && sink) ? 1.f : 0.f;
-  for (int64_t j0 = 0; j0 <= pos; j0 += SA_KEYS) {
+  const float r1 = (head_ok && rule.r1) ? rule.r1[h] : 0.f, r2 = (head_ok && rule.r1) ? rule.r2[h] : 0.f;
+  const int64_t first = (rule.window > 0 && pos - rule.window + 1 > 0) ? pos - rule.window + 1 : 0;
+  for (int64_t j0 = first; j0 <= pos; j0 += SA_KEYS) {
     const int nk = (int)min((int64_t)SA_KEYS, pos + 1 - j0);
     __syncthreads();
     for (int idx = threadIdx.x; idx < nk * dk; idx += blockDim.x) {
@@ -109,11 +134,11 @@ sink_attn_kernel(const float* __restrict__ q, const T* __restrict__ kcache, cons
       const float* qr = qs + warp * dk;
       float d = 0.f;
       for (int i = 0; i < dk; ++i) d = fmaf(qr[i], kr[i], d);
-      s = d - slope * (float)(pos - (j0 + lane));
+      s = ruled_score(d, rule, r1, r2, (float)(pos - (j0 + lane))) - slope * (float)(pos - (j0 + lane));
     }
     const float nmx = fmaxf(mx, warp_max(s));
-    const float corr = __expf(mx - nmx);                           // 0 on the first chunk without a sink (mx = -inf)
-    const float p = lane < nk ? __expf(s - nmx) : 0.f;
+    const float corr = expf(mx - nmx);                             // 0 on the first chunk without a sink (mx = -inf)
+    const float p = lane < nk ? expf(s - nmx) : 0.f;
     den = den * corr + warp_sum(p);
     mx = nmx;
 #pragma unroll
@@ -133,7 +158,40 @@ sink_attn_kernel(const float* __restrict__ q, const T* __restrict__ kcache, cons
 #pragma unroll
   for (int i = 0; i < SA_MAX_VL; ++i) {
     const int c = i * 32 + lane;
-    if (c < dv) out[t * ld_out + (int64_t)h * dv + c] = Tr<T>::from_f(acc[i] * inv);
+    if (c < dv) {
+      const float gz = rule.gate ? sigmoid_f(rule.gate[t * rule.ldg + (int64_t)h * dv + c]) : 1.f;
+      out[t * ld_out + (int64_t)h * dv + c] = Tr<T>::from_f(acc[i] * inv * gz);
+    }
+  }
+}
+
+// q and k of the windowed attention: projections [q (H dk) | k (G dk)] from column col_q of proj pass a causal convolution over
+// time (conv_w [C, taps], last tap the current token's; conv_state [rows, taps-1, C] the inputs of earlier steps, zeros before the
+// sequence's start); q_out = that * scale (fp32), the keys go to the cache.
+template <typename T>
+__global__ void window_attn_prep_kernel(const float* __restrict__ proj, int64_t ldp, int64_t col_q, const float* __restrict__ conv_w,
+                                        const float* __restrict__ conv_state, int taps, float scale, float* __restrict__ q_out,
+                                        T* __restrict__ kcache, int64_t Tcap, const int32_t* __restrict__ t_row,
+                                        const int32_t* __restrict__ t_pos, const int32_t* __restrict__ t_off, int H, int G, int dk) {
+  const int64_t t = blockIdx.x;
+  const int C = (H + G) * dk, Cq = H * dk;
+  const int row = t_row[t], pos = t_pos[t], off = t_off[t];
+  const float* pt = proj + t * ldp + col_q;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {                 // tap j multiplies the input d = taps-1-j tokens back
+      const int d = taps - 1 - j;
+      float in;
+      if (d > pos) in = 0.f;
+      else if (d <= off) in = pt[c - (int64_t)d * ldp];
+      else in = conv_state[((int64_t)row * (taps - 1) + (taps - 1 + off - d)) * C + c];
+      acc = fmaf(conv_w[(int64_t)c * taps + j], in, acc);
+    }
+    if (c < Cq) q_out[t * Cq + c] = acc * scale;
+    else if (pos < Tcap) {                           // the host sizes the cache first; never write outside it
+      const int g = (c - Cq) / dk, i = (c - Cq) % dk;
+      kcache[(((int64_t)row * G + g) * Tcap + pos) * dk + i] = Tr<T>::from_f(acc);
+    }
   }
 }
 
@@ -150,12 +208,14 @@ constexpr float LOG2E = 1.4426950408889634f;
 // blockIdx.z, and the CTA takes the blockIdx.x-th share of the key tiles (gridDim.x shares): it writes unnormalised partial
 // sums (o, running max, sum; no sink) that sink_attn_merge_kernel combines.  The keys are then read once for all heads of a
 // group, by many small CTAs at a time.
-template <typename T, int DK, int DV, bool DECODE>
+// RULED = true: the scores also pass the ScoreRule (cap, logarithmic penalty, window: tiles before the window of the CTA's first
+// row are skipped, a row whose window has not begun keeps max = -inf and adds nothing) and the output its gate.
+template <typename T, int DK, int DV, bool DECODE, bool RULED>
 __global__ void __launch_bounds__(DECODE ? 32 : ST_THREADS)
 sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, const T* __restrict__ vc, int64_t Tcap,
                       const int32_t* __restrict__ cu, const int32_t* __restrict__ rows, const int32_t* __restrict__ t_pos,
                       const float* __restrict__ sink, float slope_log2, T* __restrict__ out, int64_t ld_out, float out_scale,
-                      int H, int G, float* __restrict__ part_o, float* __restrict__ part_ms) {
+                      int H, int G, float* __restrict__ part_o, float* __restrict__ part_ms, ScoreRule rule) {
   constexpr int NT = DECODE ? 32 : ST_THREADS;
   constexpr int KROW = DK * 2, VROW = DV * 2;                       // bytes per staged row
   constexpr int K_BYTES = ST_KT * KROW, V_BYTES = ST_KT * VROW, STAGE_BYTES = K_BYTES + V_BYTES;
@@ -179,11 +239,17 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
   const int kend = DECODE ? p_first + 1 : p_first + min(n_e, q0 + ST_QT);     // keys any row of this CTA may see
   const int n_all = (kend + ST_KT - 1) / ST_KT;
   int tile_lo = 0, tile_hi = n_all;
+  if (RULED && rule.window > 0) {                                   // the first key the CTA's first row sees
+    const int first = (DECODE ? p_first : p_first + q0) - rule.window + 1;
+    tile_lo = first > 0 ? first / ST_KT : 0;
+  }
   if (DECODE) {
-    const int share = (n_all + gridDim.x - 1) / gridDim.x;
-    tile_lo = blockIdx.x * share;
+    const int share = (n_all - tile_lo + gridDim.x - 1) / gridDim.x;
+    tile_lo += blockIdx.x * share;
     tile_hi = min(n_all, tile_lo + share);
   }
+  float r1_0 = 0.f, r2_0 = 0.f, r1_1 = 0.f, r2_1 = 0.f;
+  if (RULED && rule.r1) { r1_0 = rule.r1[h0]; r2_0 = rule.r2[h0]; r1_1 = rule.r1[h1]; r2_1 = rule.r2[h1]; }
   const float slope2_0 = head_slope(slope_log2, h0, H) * LOG2E, slope2_1 = head_slope(slope_log2, h1, H) * LOG2E;
 
   uint32_t qf[DK / 16][4];
@@ -262,6 +328,14 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
 #pragma unroll
     for (int nt = 0; nt < ST_KT / 8; ++nt) {
       const int kcol = key0 + 8 * nt + 2 * qc;
+      if constexpr (RULED) {
+        const int d00 = pos0 - kcol, d01 = d00 - 1, d10 = pos1 - kcol, d11 = d10 - 1;
+        const int wnd = rule.window > 0 ? rule.window : 0x7fffffff;
+        sc[nt][0] = (d00 >= 0 && d00 < wnd) ? ruled_score(sc[nt][0], rule, r1_0, r2_0, (float)d00) : -INFINITY;
+        sc[nt][1] = (d01 >= 0 && d01 < wnd) ? ruled_score(sc[nt][1], rule, r1_0, r2_0, (float)d01) : -INFINITY;
+        sc[nt][2] = (d10 >= 0 && d10 < wnd) ? ruled_score(sc[nt][2], rule, r1_1, r2_1, (float)d10) : -INFINITY;
+        sc[nt][3] = (d11 >= 0 && d11 < wnd) ? ruled_score(sc[nt][3], rule, r1_1, r2_1, (float)d11) : -INFINITY;
+      }
       sc[nt][0] = kcol <= pos0 ? fmaf(sc[nt][0], LOG2E, -slope2_0 * (float)(pos0 - kcol)) : -INFINITY;
       sc[nt][1] = kcol + 1 <= pos0 ? fmaf(sc[nt][1], LOG2E, -slope2_0 * (float)(pos0 - kcol - 1)) : -INFINITY;
       sc[nt][2] = kcol <= pos1 ? fmaf(sc[nt][2], LOG2E, -slope2_1 * (float)(pos1 - kcol)) : -INFINITY;
@@ -272,9 +346,14 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
     t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 1)); t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 2));
     t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 1)); t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 2));
     // finite from a CTA's first tile on: its first key is inside every row's bound (prompts: key 0; decode: one position)
-    const float mn0 = fmaxf(m0, t0), mn1 = fmaxf(m1, t1);
+    float mn0 = fmaxf(m0, t0), mn1 = fmaxf(m1, t1);
+    const float keep0 = mn0, keep1 = mn1;
+    if constexpr (RULED) {                           // nothing seen yet (the row's window begins later): exponentials against 0
+      if (mn0 == -INFINITY) mn0 = 0.f;
+      if (mn1 == -INFINITY) mn1 = 0.f;
+    }
     const float corr0 = exp2f(m0 - mn0), corr1 = exp2f(m1 - mn1);
-    m0 = mn0; m1 = mn1;
+    m0 = keep0; m1 = keep1;
     float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
     for (int nt = 0; nt < ST_KT / 8; ++nt) {
@@ -327,11 +406,18 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
   const float inv0 = out_scale / s0, inv1 = out_scale / s1;
   T* o0 = out + (int64_t)tk0 * ld_out + (int64_t)h0 * DV;
   T* o1 = out + (int64_t)tk1 * ld_out + (int64_t)h1 * DV;
+  const float* g0 = (RULED && rule.gate) ? rule.gate + (int64_t)tk0 * rule.ldg + (int64_t)h0 * DV : nullptr;
+  const float* g1 = (RULED && rule.gate) ? rule.gate + (int64_t)tk1 * rule.ldg + (int64_t)h1 * DV : nullptr;
 #pragma unroll
   for (int j = 0; j < DV / 8; ++j) {
     const int c = 8 * j + 2 * qc;
-    if (l0 < n_e) *reinterpret_cast<uint32_t*>(o0 + c) = pack2<T>(o[j][0] * inv0, o[j][1] * inv0);
-    if (l1 < n_e) *reinterpret_cast<uint32_t*>(o1 + c) = pack2<T>(o[j][2] * inv1, o[j][3] * inv1);
+    float a0 = o[j][0] * inv0, a1 = o[j][1] * inv0, b0 = o[j][2] * inv1, b1 = o[j][3] * inv1;
+    if (RULED && g0) {
+      if (l0 < n_e) { a0 *= sigmoid_f(g0[c]); a1 *= sigmoid_f(g0[c + 1]); }
+      if (l1 < n_e) { b0 *= sigmoid_f(g1[c]); b1 *= sigmoid_f(g1[c + 1]); }
+    }
+    if (l0 < n_e) *reinterpret_cast<uint32_t*>(o0 + c) = pack2<T>(a0, a1);
+    if (l1 < n_e) *reinterpret_cast<uint32_t*>(o1 + c) = pack2<T>(b0, b1);
   }
 }
 
@@ -339,7 +425,8 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
 template <typename T>
 __global__ void sink_attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ms,
                                        const int32_t* __restrict__ cu, const float* __restrict__ sink, T* __restrict__ out,
-                                       int64_t ld_out, float out_scale, int H, int dv, int splits) {
+                                       int64_t ld_out, float out_scale, int H, int dv, int splits, const float* __restrict__ gate,
+                                       int64_t ldg) {
   const int e = blockIdx.x, h = blockIdx.y;
   if (cu[e + 1] - cu[e] <= 0) return;
   const int64_t base = ((int64_t)e * H + h) * splits;
@@ -357,20 +444,22 @@ __global__ void sink_attn_merge_kernel(const float* __restrict__ part_o, const f
       const float ms = part_ms[(base + sidx) * 2];
       if (ms != -INFINITY) a = fmaf(part_o[(base + sidx) * dv + c], exp2f(ms - m), a);
     }
-    out[(int64_t)cu[e] * ld_out + (int64_t)h * dv + c] = Tr<T>::from_f(a * inv);
+    const float gz = gate ? sigmoid_f(gate[(int64_t)cu[e] * ldg + (int64_t)h * dv + c]) : 1.f;
+    out[(int64_t)cu[e] * ld_out + (int64_t)h * dv + c] = Tr<T>::from_f(a * inv * gz);
   }
 }
 
 constexpr int SINK_ATTN_MAX_SPLITS = 16;
 
-template <typename T, int DK, int DV>
+template <typename T, int DK, int DV, bool RULED>
 static int sink_attn_tiles_launch(const float* q, const void* kc, const void* vc, int64_t Tcap, const int32_t* cu, const int32_t* rows,
                                   const int32_t* t_pos, const float* sink, float slope_log2, void* out, int64_t ld_out,
-                                  float out_scale, int nb, int max_n, int H, int G, float* ws, size_t ws_bytes, cudaStream_t st) {
+                                  float out_scale, int nb, int max_n, int H, int G, float* ws, size_t ws_bytes, cudaStream_t st,
+                                  const ScoreRule& rule) {
   constexpr int smem = ST_STAGES * ST_KT * (DK + DV) * 2;
   if (max_n == 1) {
     // decode: shares of the key tiles per (entry, key/value head), as many as keep several CTAs per SM busy and the workspace holds
-    auto kern = sink_attn_tile_kernel<T, DK, DV, true>;
+    auto kern = sink_attn_tile_kernel<T, DK, DV, true, RULED>;
     static bool attr_set = false;
     if (smem > 48 * 1024 && !attr_set) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -386,14 +475,14 @@ static int sink_attn_tiles_launch(const float* q, const void* kc, const void* vc
     float* part_ms = ws + (size_t)nb * H * splits * DV;
     dim3 grid((unsigned)splits, (unsigned)G, (unsigned)nb);
     kern<<<grid, 32, smem, st>>>(q, (const T*)kc, (const T*)vc, Tcap, cu, rows, t_pos, sink, slope_log2, (T*)out, ld_out, out_scale,
-                                 H, G, part_o, part_ms);
+                                 H, G, part_o, part_ms, rule);
     B200P_LAUNCH_CHECK("sink_attn_tile_kernel");
     sink_attn_merge_kernel<T><<<dim3((unsigned)nb, (unsigned)H), DV >= 128 ? 128 : 64, 0, st>>>(part_o, part_ms, cu, sink, (T*)out, ld_out,
-                                                                                                   out_scale, H, DV, splits);
+                                                                                                   out_scale, H, DV, splits, rule.gate, rule.ldg);
     B200P_LAUNCH_CHECK("sink_attn_merge_kernel");
     return B200P_OK;
   }
-  auto kern = sink_attn_tile_kernel<T, DK, DV, false>;
+  auto kern = sink_attn_tile_kernel<T, DK, DV, false, RULED>;
   if (smem > 48 * 1024) {
     static bool attr_set = false;
     if (!attr_set) {
@@ -404,7 +493,7 @@ static int sink_attn_tiles_launch(const float* q, const void* kc, const void* vc
   }
   dim3 grid((unsigned)((max_n + ST_QT - 1) / ST_QT), (unsigned)H, (unsigned)nb);
   kern<<<grid, ST_THREADS, smem, st>>>(q, (const T*)kc, (const T*)vc, Tcap, cu, rows, t_pos, sink, slope_log2, (T*)out, ld_out,
-                                       out_scale, H, G, nullptr, nullptr);
+                                       out_scale, H, G, nullptr, nullptr, rule);
   B200P_LAUNCH_CHECK("sink_attn_tile_kernel");
   return B200P_OK;
 }
@@ -417,15 +506,24 @@ static bool sink_attn_tiles_ok(int dk, int dv, int dtype) {
 template <typename T>
 static int sink_attn_tiles(const float* q, const void* kc, const void* vc, int64_t Tcap, const int32_t* cu, const int32_t* rows,
                            const int32_t* t_pos, const float* sink, float slope_log2, void* out, int64_t ld_out, float out_scale,
-                           int nb, int max_n, int H, int G, int dk, int dv, float* ws, size_t ws_bytes, cudaStream_t st) {
+                           int nb, int max_n, int H, int G, int dk, int dv, float* ws, size_t ws_bytes, cudaStream_t st,
+                           const ScoreRule* rule) {
+  static const ScoreRule none = {0.f, nullptr, nullptr, 0, nullptr, 0};
 #define ST_CASE(DK_, DV_) \
-  if (dk == DK_ && dv == DV_) \
-    return sink_attn_tiles_launch<T, DK_, DV_>(q, kc, vc, Tcap, cu, rows, t_pos, sink, slope_log2, out, ld_out, out_scale, nb, max_n, H, G, ws, ws_bytes, st)
+  if (dk == DK_ && dv == DV_ && !rule) \
+    return sink_attn_tiles_launch<T, DK_, DV_, false>(q, kc, vc, Tcap, cu, rows, t_pos, sink, slope_log2, out, ld_out, out_scale, nb, max_n, H, G, ws, ws_bytes, st, none)
+#define ST_RULED(DK_, DV_) \
+  if (dk == DK_ && dv == DV_ && rule) \
+    return sink_attn_tiles_launch<T, DK_, DV_, true>(q, kc, vc, Tcap, cu, rows, t_pos, sink, slope_log2, out, ld_out, out_scale, nb, max_n, H, G, ws, ws_bytes, st, *rule)
   ST_CASE(64, 64);
   ST_CASE(64, 128);
   ST_CASE(128, 64);
   ST_CASE(128, 128);
+  ST_RULED(64, 64);
+  ST_RULED(128, 128);
+  if (rule) return 1;                                            // other sizes with a rule: the caller takes the per-token kernel
 #undef ST_CASE
+#undef ST_RULED
   set_error("tile attention: unsupported sizes");
   return B200P_ERR_ARG;
 }
@@ -453,7 +551,8 @@ extern "C" int b200p_sink_attn_prep(const float* proj, int64_t ldp, int64_t col_
 template <typename T>
 static int sink_attn_generic(const float* q, const void* kcache, const void* vcache, int64_t Tcap, const int32_t* t_row,
                              const int32_t* t_pos, const float* sink, float slope_log2, void* out, int64_t ld_out, float out_scale,
-                             int64_t M, int H, int G, int dk, int dv, cudaStream_t st) {
+                             int64_t M, int H, int G, int dk, int dv, cudaStream_t st, const ScoreRule* rule = nullptr) {
+  static const ScoreRule none = {0.f, nullptr, nullptr, 0, nullptr, 0};
   const int per = H / G, nw = per < SA_MAX_HEADS ? per : SA_MAX_HEADS;
   const size_t smem = ((size_t)SA_KEYS * (dk + 1) + (size_t)SA_KEYS * dv + (size_t)nw * dk) * sizeof(float);
   auto kern = sink_attn_kernel<T>;
@@ -463,7 +562,7 @@ static int sink_attn_generic(const float* q, const void* kcache, const void* vca
   }
   dim3 grid((unsigned)M, (unsigned)G, (unsigned)((per + nw - 1) / nw));
   kern<<<grid, nw * 32, smem, st>>>(q, (const T*)kcache, (const T*)vcache, Tcap, t_row, t_pos, sink, slope_log2, (T*)out, ld_out,
-                                    out_scale, H, G, dk, dv);
+                                    out_scale, H, G, dk, dv, rule ? *rule : none);
   B200P_LAUNCH_CHECK("sink_attn_kernel");
   return B200P_OK;
 }
@@ -474,10 +573,11 @@ extern "C" size_t b200p_sink_attn_workspace_bytes(int64_t nb, int H, int dv) {
   return (size_t)nb * H * SINK_ATTN_MAX_SPLITS * (dv + 2) * sizeof(float);
 }
 
-extern "C" int b200p_sink_attn(const float* q, const void* kcache, const void* vcache, int64_t Tcap, const int32_t* t_row,
-                               const int32_t* t_pos, const int32_t* cu, const int32_t* rows, int nb, int max_n, const float* sink,
-                               float slope_log2, void* out, int64_t ld_out, float out_scale, int64_t M, int H, int G, int dk,
-                               int dv, int dtype, void* workspace, size_t workspace_bytes, void* stream) {
+// the shared body of b200p_sink_attn and b200p_window_attn
+static int attn_dispatch(const float* q, const void* kcache, const void* vcache, int64_t Tcap, const int32_t* t_row,
+                         const int32_t* t_pos, const int32_t* cu, const int32_t* rows, int nb, int max_n, const float* sink,
+                         float slope_log2, void* out, int64_t ld_out, float out_scale, int64_t M, int H, int G, int dk, int dv,
+                         int dtype, void* workspace, size_t workspace_bytes, void* stream, const ScoreRule* rule) {
   B200P_REQUIRE(q && kcache && vcache && t_row && t_pos && out, B200P_ERR_ARG, "null pointer");
   B200P_REQUIRE(H > 0 && G > 0 && H % G == 0 && G < 65536 && dk > 0 && dv > 0, B200P_ERR_ARG, "bad head geometry");
   B200P_REQUIRE(dv <= 32 * SA_MAX_VL && dk <= 1024, B200P_ERR_ARG, "value size above %d or key size above 1024 is not built",
@@ -493,15 +593,50 @@ extern "C" int b200p_sink_attn(const float* q, const void* kcache, const void* v
       aligned(kcache, 16) && aligned(vcache, 16) && aligned(out, 4) && aligned(q, 8) && nb < 65536 && H < 65536) {
     const int rc = dtype == B200P_F16
         ? sink_attn_tiles<__half>(q, kcache, vcache, Tcap, cu, rows, t_pos, sink, slope_log2, out, ld_out, out_scale, nb, max_n, H, G, dk, dv,
-                                  (float*)workspace, workspace_bytes, st)
+                                  (float*)workspace, workspace_bytes, st, rule)
         : sink_attn_tiles<__nv_bfloat16>(q, kcache, vcache, Tcap, cu, rows, t_pos, sink, slope_log2, out, ld_out, out_scale, nb, max_n, H, G,
-                                         dk, dv, (float*)workspace, workspace_bytes, st);
+                                         dk, dv, (float*)workspace, workspace_bytes, st, rule);
     if (rc != 1) return rc;
   }
   switch (dtype) {
-    case B200P_F32: return sink_attn_generic<float>(q, kcache, vcache, Tcap, t_row, t_pos, sink, slope_log2, out, ld_out, out_scale, M, H, G, dk, dv, st);
-    case B200P_F16: return sink_attn_generic<__half>(q, kcache, vcache, Tcap, t_row, t_pos, sink, slope_log2, out, ld_out, out_scale, M, H, G, dk, dv, st);
-    case B200P_BF16: return sink_attn_generic<__nv_bfloat16>(q, kcache, vcache, Tcap, t_row, t_pos, sink, slope_log2, out, ld_out, out_scale, M, H, G, dk, dv, st);
+    case B200P_F32: return sink_attn_generic<float>(q, kcache, vcache, Tcap, t_row, t_pos, sink, slope_log2, out, ld_out, out_scale, M, H, G, dk, dv, st, rule);
+    case B200P_F16: return sink_attn_generic<__half>(q, kcache, vcache, Tcap, t_row, t_pos, sink, slope_log2, out, ld_out, out_scale, M, H, G, dk, dv, st, rule);
+    case B200P_BF16: return sink_attn_generic<__nv_bfloat16>(q, kcache, vcache, Tcap, t_row, t_pos, sink, slope_log2, out, ld_out, out_scale, M, H, G, dk, dv, st, rule);
     default: set_error("bad dtype %d", dtype); return B200P_ERR_ARG;
   }
+}
+
+extern "C" int b200p_sink_attn(const float* q, const void* kcache, const void* vcache, int64_t Tcap, const int32_t* t_row,
+                               const int32_t* t_pos, const int32_t* cu, const int32_t* rows, int nb, int max_n, const float* sink,
+                               float slope_log2, void* out, int64_t ld_out, float out_scale, int64_t M, int H, int G, int dk,
+                               int dv, int dtype, void* workspace, size_t workspace_bytes, void* stream) {
+  return attn_dispatch(q, kcache, vcache, Tcap, t_row, t_pos, cu, rows, nb, max_n, sink, slope_log2, out, ld_out, out_scale, M, H, G, dk,
+                       dv, dtype, workspace, workspace_bytes, stream, nullptr);
+}
+
+extern "C" int b200p_window_attn_prep(const float* proj, int64_t ldp, int64_t col_q, const float* conv_w, const float* conv_state,
+                                      int taps, float scale, float* q_out, void* kcache, int64_t Tcap, const int32_t* t_row,
+                                      const int32_t* t_pos, const int32_t* t_off, int64_t M, int H, int G, int dk, int dtype,
+                                      void* stream) {
+  B200P_REQUIRE(proj && conv_w && q_out && kcache && t_row && t_pos && t_off, B200P_ERR_ARG, "null pointer");
+  B200P_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && taps >= 1 && (taps == 1 || conv_state), B200P_ERR_ARG,
+                "bad head geometry, or a convolution without its carried inputs");
+  if (M == 0) return B200P_OK;
+  B200P_DISPATCH_DTYPE(dtype, T, (window_attn_prep_kernel<T><<<(unsigned)M, 256, 0, (cudaStream_t)stream>>>(
+      proj, ldp, col_q, conv_w, conv_state, taps, scale, q_out, (T*)kcache, Tcap, t_row, t_pos, t_off, H, G, dk)));
+  B200P_LAUNCH_CHECK("window_attn_prep_kernel");
+  return B200P_OK;
+}
+
+extern "C" int b200p_window_attn(const float* q, const void* kcache, const void* vcache, int64_t Tcap, const int32_t* t_row,
+                                 const int32_t* t_pos, const int32_t* cu, const int32_t* rows, int nb, int max_n, float softcap,
+                                 const float* r1, const float* r2, int64_t window, const float* gate, int64_t ldg, void* out,
+                                 int64_t ld_out, int64_t M, int H, int G, int dk, int dv, int dtype, void* workspace,
+                                 size_t workspace_bytes, void* stream) {
+  B200P_REQUIRE((r1 == nullptr) == (r2 == nullptr), B200P_ERR_ARG, "the distance penalty needs both of its vectors");
+  B200P_REQUIRE(window >= 0 && window < 0x7fffffff && softcap >= 0.f, B200P_ERR_ARG, "bad window or cap");
+  B200P_REQUIRE(gate == nullptr || ldg >= (int64_t)H * dv, B200P_ERR_ARG, "gate rows are shorter than the heads");
+  const ScoreRule rule = {softcap, r1, r2, (int)window, gate, ldg};
+  return attn_dispatch(q, kcache, vcache, Tcap, t_row, t_pos, cu, rows, nb, max_n, nullptr, 0.f, out, ld_out, 1.f, M, H, G, dk, dv, dtype,
+                       workspace, workspace_bytes, stream, &rule);
 }

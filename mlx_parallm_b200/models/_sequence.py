@@ -23,13 +23,19 @@ layers mix a recurrent state with windowed attention over a shared low-rank late
                             over the chosen logits, or sigmoid scores picked inside
                             the best expert groups with a gated shared expert
     LatentAttention         queries and keys/values through low-rank latents,       b200p_latent_prep / b200p_latent_attn
-                            sliding window, optional sharing of another layer's latents
+                            sliding window, optional sharing of another layer's latents,  b200p_latent_rope_prep / _q_rope
+                            optionally a rotated key part shared by the heads
+    WindowAttention         grouped-head attention without rotation over a sliding    b200p_window_attn_prep / b200p_window_attn
+                            window: short convolutions on q and k, values that are the
+                            keys, capped scores, logarithmic distance penalty, output gate
     ClampedGLU              g * sigmoid(1.702 g) * (u + 1) on clamped gate / up      b200p_gemm (fused epilogue)
     TokenSideInput          a small per-layer table indexed by the token, gated      b200p_token_gate
     SequenceModel           the layer chain over a ragged batch: norm -> sublayer -> norm -> residual (b200p_norm_add_norm), or
                             one norm feeding a mixer and a feed-forward that are added together, or a norm before each of the
                             two, with an optional span of layers that runs several times on the same weights
-                            (b200p_residual_add_norm)
+                            (b200p_residual_add_norm), or several copies of the stream that every sublayer reads as a weighted sum
+                            and writes back through a mixing matrix, with a tanh norm and a short convolution on what a sublayer
+                            reads (b200p_hyper_step / b200p_canon_conv)
 
 A step is a ragged batch: entry e brings ``counts[e]`` tokens for cache row ``rows[e]``; prompts of different lengths are
 packed back to back (no padding), decode steps bring one token per live row.  Every kernel works from the per-token plan
@@ -49,7 +55,7 @@ import math
 
 from .._lib import (GATE_SIGMOID, GATE_SILU, GEMM_GLU_CLAMP, GEMM_GLU_GELU_TANH, GEMM_GLU_SILU, GEMM_RELU_SQ, GEMM_STORE, GEMM_STORE_F32,
                     SCAN_ACCUMULATE, SCAN_DELTA, SCAN_DELTA_CHANNEL)
-from .base import BatchedKVCache, DeltaRuleState, LatentKVCache, RowState, StateGroup, TokenState
+from .base import BatchedKVCache, ConvTailState, DeltaRuleState, LatentKVCache, RowState, StateGroup, TokenState
 
 MAX_TOKENS_PER_FORWARD = 8192     # packed tokens of one pass through the layers
 
@@ -462,29 +468,41 @@ class LatentAttention:
     k = W_uk c, v = W_uv c per head.  Here the up-projections are folded around the attention: the query is carried into
     the latent space (W_uk^T q per head), the heads attend over c itself, and W_uv is applied to the attended latent.
     ``window`` > 0: position i sees j with 0 <= i - j < window.  ``kv_from``: index of the earlier layer whose latents this
-    layer reads (it then has no W_dkv of its own)."""
+    layer reads (it then has no W_dkv of its own).
+
+    ``rot_dim`` > 0: every head's query is [dim unrotated | rot_dim rotated] and W_dkv has rot_dim more rows, one rotated key
+    part that all heads share; the pairs (2i, 2i+1) of the rotated parts turn by position * rates[i] and are multiplied by
+    ``mag``; score = (q_unrotated . k_unrotated + q_rotated . k_rotated) * scale.  The cache row is then
+    [latent | rotated key part | zeros up to a multiple of 32] and the query row in latent space [W_uk^T q | rotated q | zeros], so
+    the same attention kernels score and attend over whole rows; W_uv reads the first kv_rank columns of the attended row."""
 
     def __init__(self, width: int, heads: int, dim: int, vdim: int, q_rank: int, kv_rank: int, scale: float, window: int,
-                 eps: float, kv_from: Optional[int] = None):
+                 eps: float, kv_from: Optional[int] = None, rot_dim: int = 0, rates: Sequence[float] = (), mag: float = 1.0):
         self.width, self.heads, self.dim, self.vdim = width, heads, dim, vdim
         self.q_rank, self.kv_rank, self.scale, self.window, self.eps, self.kv_from = q_rank, kv_rank, scale, window, eps, kv_from
         self.own_kv = kv_from is None
-        self.down = Linear(width, q_rank + (kv_rank if self.own_kv else 0))      # rows [dq | dkv]
-        self.uq = Linear(q_rank, heads * dim)
+        self.rot_dim, self.rate_values, self.mag = int(rot_dim), [float(r) for r in rates], float(mag)
+        if self.rot_dim:
+            if kv_from is not None or self.rot_dim % 2 or 2 * len(self.rate_values) != self.rot_dim:
+                raise ValueError("a rotated key part needs the layer's own latents, an even size and one rate per pair")
+        self.row = (kv_rank + self.rot_dim + 31) // 32 * 32 if self.rot_dim else kv_rank      # values per cache row
+        self.rates: Optional[torch.Tensor] = None         # fp32 on the device
+        self.down = Linear(width, q_rank + (kv_rank + self.rot_dim if self.own_kv else 0))      # rows [dq | dkv]
+        self.uq = Linear(q_rank, heads * (dim + self.rot_dim))
         self.uk_t: Optional[torch.Tensor] = None          # [heads, kv_rank, dim]: W_uk per head, transposed
         self.uv: Optional[torch.Tensor] = None            # [heads * vdim, kv_rank]
         self.o_proj = Linear(heads * vdim, width)
         self.q_norm_w = self.kv_norm_w = None             # fp32
 
     def new_state(self, batch_size: int) -> RowState:
-        return LatentKVCache(self.kv_rank, batch_size) if self.own_kv else RowState(batch_size)
+        return LatentKVCache(self.row, batch_size) if self.own_kv else RowState(batch_size)
 
     def reserve(self, s: Scratch, dt):
         s.reserve("proj", torch.float32, self.down.out_features)
         s.reserve("cq", dt, self.q_rank)
-        s.reserve("q", dt, self.heads * self.dim)
-        s.reserve("qlat", torch.float32, self.heads * self.kv_rank)
-        s.reserve("olat", dt, self.heads * self.kv_rank)
+        s.reserve("q", dt, self.heads * (self.dim + self.rot_dim))
+        s.reserve("qlat", torch.float32, self.heads * self.row)
+        s.reserve("olat", dt, self.heads * self.row)
         s.reserve("mix", dt, self.heads * self.vdim)
 
     def __call__(self, x, y_out, st: RowState, plan: dict, s: Scratch, caches):
@@ -492,6 +510,21 @@ class LatentAttention:
         H, R, dk, dv = self.heads, self.kv_rank, self.dim, self.vdim
         proj = self.down(x, GEMM_STORE_F32, out=s.get("proj", f32, M, self.down.out_features))
         cq = s.get("cq", dt, M, self.q_rank)
+        if self.rot_dim:
+            dr, row = self.rot_dim, self.row
+            ops.latent_rope_prep(proj, self.q_rank, R, dr, self.q_norm_w, self.kv_norm_w, self.eps, self.rates, self.mag, cq, st.latent,
+                                 plan["t_row"], plan["t_pos"])
+            q = self.uq(cq, GEMM_STORE, out=s.get("q", dt, M, H * (dk + dr)))
+            qlat = s.get("qlat", f32, M, H * row)
+            ops.gemm(q, self.uk_t, GEMM_STORE_F32, out=qlat, batch=H, strides=(dk + dr, R * dk, row), M=M, N=R, K=dk, ldx=H * (dk + dr),
+                     ldw=dk, ldy=H * row)
+            ops.latent_q_rope(q, H, dk, dr, R, self.rates, self.mag, plan["t_pos"], qlat)
+            olat = s.get("olat", dt, M, H * row)
+            ops.latent_attn(qlat, st.latent, plan["t_row"], plan["t_pos"], olat, H, row, self.window, self.scale, cu=plan["cu"],
+                            rows=plan["rows"], nb=plan["nb"], max_n=plan["max_n"])
+            mix = s.get("mix", dt, M, H * dv)
+            ops.gemm(olat, self.uv, GEMM_STORE, out=mix, batch=H, strides=(row, dv * R, dv), M=M, N=dv, K=R, ldx=H * row, ldw=R, ldy=H * dv)
+            return self.o_proj(mix, GEMM_STORE_F32, out=y_out)
         cache = st if self.own_kv else caches[self.kv_from]
         ops.latent_prep(proj, self.q_rank, R, self.q_norm_w, self.kv_norm_w, self.eps, cq, cache.latent if self.own_kv else None,
                         plan["t_row"], plan["t_pos"])
@@ -504,6 +537,58 @@ class LatentAttention:
                         rows=plan["rows"], nb=plan["nb"], max_n=plan["max_n"])
         mix = s.get("mix", dt, M, H * dv)
         ops.gemm(olat, self.uv, GEMM_STORE, out=mix, batch=H, strides=(R, dv * R, dv), M=M, N=dv, K=R, ldx=H * R, ldw=R, ldy=H * dv)
+        return self.o_proj(mix, GEMM_STORE_F32, out=y_out)
+
+
+class WindowAttention:
+    """Causal attention without rotation: ``heads`` query heads over ``kv_heads`` key heads of ``dim`` (query head h reads
+    h // (heads // kv_heads)); the values are the keys, so one buffer is cached.  q and k pass a causal convolution of ``taps``
+    taps over time right after their projections (the last taps - 1 projected values of a sequence are carried as state).
+    score = q . k * scale; ``softcap`` > 0: score <- softcap tanh(score / softcap); ``distance_penalty``: minus
+    r1_h ln(1 + r2_h (i - j)) with two numbers per head; ``window`` > 0: position i sees j with 0 <= i - j < window; softmax;
+    ``gated``: the heads' outputs are multiplied by sigmoid(W_g x) before the output projection.  Projection rows [q | k | gate]."""
+
+    DECODE_WS_ROWS = 256
+
+    def __init__(self, width: int, heads: int, kv_heads: int, dim: int, scale: float, taps: int = 1, softcap: float = 0.0,
+                 window: int = 0, distance_penalty: bool = False, gated: bool = False):
+        if heads % kv_heads:
+            raise ValueError("heads must be a multiple of kv_heads")
+        self.width, self.heads, self.kv_heads, self.dim, self.scale, self.taps = width, heads, kv_heads, dim, float(scale), int(taps)
+        self.softcap, self.window, self.distance_penalty, self.gated = float(softcap), int(window), bool(distance_penalty), bool(gated)
+        self.conv_channels = (heads + kv_heads) * dim
+        self.n_mix = heads * dim
+        self.col_g = self.conv_channels
+        self.n_proj = self.conv_channels + (self.n_mix if gated else 0)
+        self.in_proj = Linear(width, self.n_proj)
+        self.o_proj = Linear(self.n_mix, width)
+        self.conv_w = self.r1 = self.r2 = None                 # fp32
+
+    def new_state(self, batch_size: int) -> RowState:
+        return StateGroup([BatchedKVCache(self.dim, self.kv_heads, batch_size, values_are_keys=True),
+                           ConvTailState(self.conv_channels, self.taps, batch_size)], batch_size)
+
+    def reserve(self, s: Scratch, dt):
+        s.reserve("proj", torch.float32, self.n_proj)
+        s.reserve("aq", torch.float32, self.n_mix)
+        s.reserve("mix", dt, self.n_mix)
+        if dt != torch.float32:
+            s.reserve_flat("attn_ws", torch.float32, ops.sink_attn_workspace_floats(min(s.rows, self.DECODE_WS_ROWS), self.heads, self.dim))
+
+    def __call__(self, x, y_out, st: StateGroup, plan: dict, s: Scratch, caches):
+        M, dt, f32 = x.shape[0], x.dtype, torch.float32
+        kv, tail = st.parts
+        proj = self.in_proj(x, GEMM_STORE_F32, out=s.get("proj", f32, M, self.n_proj))
+        q = s.get("aq", f32, M, self.n_mix)
+        ops.window_attn_prep(proj, 0, self.conv_w, tail.conv, self.taps, self.scale, q, kv.keys, plan["t_row"], plan["t_pos"], plan["t_off"],
+                             self.heads, self.kv_heads, self.dim)
+        if self.taps > 1:
+            ops.delta_conv_commit(proj, tail.conv, plan["cu"], plan["rows"], plan["nb"], self.conv_channels, self.taps)
+        mix = s.get("mix", dt, M, self.n_mix)
+        ops.window_attn(q, kv.keys, kv.keys, plan["t_row"], plan["t_pos"], mix, self.heads, self.kv_heads, self.dim, self.dim,
+                        softcap=self.softcap, r1=self.r1 if self.distance_penalty else None, r2=self.r2 if self.distance_penalty else None,
+                        window=self.window, gate=proj[:, self.col_g:] if self.gated else None, cu=plan["cu"], rows=plan["rows"],
+                        nb=plan["nb"], max_n=plan["max_n"], workspace=s.flat("attn_ws", f32) if dt != f32 else None)
         return self.o_proj(mix, GEMM_STORE_F32, out=y_out)
 
 
@@ -564,6 +649,9 @@ class RoutedExperts:
       "sigmoid"  scores s = sigmoid(W_r x); experts are picked by s + correction (a vector per layer) among the experts of the
                  ``groups[1]`` best of ``groups[0]`` equal groups of neighbouring experts (a group's score: the sum of its two
                  largest picking scores); weights s / sum(chosen s) * ``route_scale``.
+      "scores"   the ``top`` largest s = sigmoid(W_r x) chosen, their weights those scores as they are.
+    ``weight_on`` "input": the weight multiplies what the expert reads, y = sum expert_k(w_k x), instead of its output.
+    ``limit``: the clamp of experts with the "clamped" unit.
     ``shared_gate``: the shared expert's output is multiplied by sigmoid(w_sg . x), one number per token (w_sg is stacked under
     the router's rows, so the router's product yields it).
     The tokens are sorted by expert on the device and every expert multiplies its own contiguous rows (grouped GEMMs), so the
@@ -571,10 +659,13 @@ class RoutedExperts:
 
     def __init__(self, width: int, experts: int, top: int, ff: int, act: str, shared_ff: int = 0, shared_act: Optional[str] = None,
                  router_bias: bool = True, scoring: str = "softmax", groups: Sequence[int] = (1, 1), route_scale: float = 1.0,
-                 shared_gate: bool = False):
-        if scoring not in ("softmax", "sigmoid"):
+                 shared_gate: bool = False, weight_on: str = "output", limit: float = 0.0):
+        if scoring not in ("softmax", "sigmoid", "scores"):
             raise ValueError(f"unknown expert scoring {scoring!r}")
+        if weight_on not in ("output", "input"):
+            raise ValueError(f"the routing weight goes on the experts' output or input, not {weight_on!r}")
         self.width, self.experts, self.top, self.ff = width, experts, top, ff
+        self.weight_on, self.limit = weight_on, float(limit)
         self.scoring, self.groups, self.route_scale = scoring, (int(groups[0]), int(groups[1])), float(route_scale)
         self.shared_gate = bool(shared_gate and shared_ff)
         self.epilogue = GatedFF.EPILOGUES[act]
@@ -615,19 +706,25 @@ class RoutedExperts:
         ids, wts = s.get("moe_ids", i32, M, self.top), s.get("moe_wts", f32, M, self.top)
         slot_of, token_of = s.get("moe_slot", i32, M, self.top), s.get("moe_tok", i32, M, self.top)
         seg = s.flat("moe_seg", i32)
-        if self.scoring == "sigmoid":
+        if self.scoring == "scores":
+            ops.moe_route_scores(logits, ids, wts, seg, slot_of, token_of, self.top, experts=self.experts)
+        elif self.scoring == "sigmoid":
             ops.moe_route_sigmoid(logits, self.router_bias, ids, wts, seg, slot_of, token_of, self.top, self.groups[0], self.groups[1],
                                   self.route_scale, experts=self.experts)
         else:
             ops.moe_route(logits, self.router_bias, ids, wts, seg, slot_of, token_of, self.top)
         xs = s.get("moe_x", dt, n, self.width)
-        ops.moe_gather(x, token_of, xs)
-        act = ops.gemm_grouped(xs, self.gate_up, seg, M, self.epilogue, out=s.get("moe_act", dt, n, self.ff))
+        on_input = self.weight_on == "input"
+        if on_input:
+            ops.moe_scatter_scaled(x, slot_of, wts, xs, self.top)
+        else:
+            ops.moe_gather(x, token_of, xs)
+        act = ops.gemm_grouped(xs, self.gate_up, seg, M, self.epilogue, out=s.get("moe_act", dt, n, self.ff), limit=self.limit)
         ye = ops.gemm_grouped(act, self.down, seg, M, GEMM_STORE_F32, out=s.get("moe_y", f32, n, self.width))
         ysh = None
         if self.shared is not None:
             ysh = self.shared(x, s.get("y_shared", f32, M, self.width), s)
-        ops.moe_combine(ye, slot_of, wts, ysh, y_out, self.top, shared_gate=logits[:, self.experts:self.experts + 1] if self.shared_gate else None)
+        ops.moe_combine(ye, slot_of, None if on_input else wts, ysh, y_out, self.top, shared_gate=logits[:, self.experts:self.experts + 1] if self.shared_gate else None)
         return y_out
 
 
@@ -681,8 +778,20 @@ class LayerRun:
     def __init__(self, layer: int, slot: int, mixer, mlp, norm_w_name: str, opens: bool = False, norm2_w_name: Optional[str] = None):
         self.layer, self.slot, self.mixer, self.mlp, self.norm_w_name, self.opens = layer, slot, mixer, mlp, norm_w_name, opens
         self.norm2_w_name = norm2_w_name
+        self.port1: Optional[StreamPort] = None       # "hyper" chain: how the mixer and the feed-forward meet the stream's copies
+        self.port2: Optional[StreamPort] = None
         self.norm_w: Optional[torch.Tensor] = None
         self.norm2_w: Optional[torch.Tensor] = None
+
+
+class StreamPort:
+    """How one sublayer of a "hyper" model meets the copies of the residual stream: it reads u = sum_s read[s] x_s, norms it with
+    tanh(alpha u) w + b, adds the causal convolution ``conv_w`` [width, taps] of that over time, and its output y is written back
+    as x_r <- sum_s mix[s, r] x_s + out[r] y.  All fp32 on the device."""
+
+    def __init__(self, norm_name: str, hc_name: str, conv_name: str):
+        self.norm_name, self.hc_name, self.conv_name = norm_name, hc_name, conv_name
+        self.read = self.out = self.mix = self.alpha = self.w = self.b = self.conv_w = None
 
 
 def unroll_layers(n_layers: int, start: int = 0, stop: int = 0, times: int = 1) -> List[tuple]:
@@ -701,8 +810,10 @@ class SequenceModel:
     ``self.final_norm_w`` / ``self.lm_head``, name their tensors in ``load_weights``, and describe their layers in one of two
     ways: ``block_style`` "sandwich": ``self.sublayers`` (in execution order) and ``self.mixers`` (one per layer), every
     sublayer between two norms; "parallel": ``self.runs`` (LayerRun, in execution order) and optionally ``self.loop_in``;
-    "prenorm": ``self.runs`` whose mixer and feed-forward each read a norm of their own.  ``self.logit_scale`` multiplies
-    the logits."""
+    "prenorm": ``self.runs`` whose mixer and feed-forward each read a norm of their own; "hyper": ``self.runs`` with a
+    ``StreamPort`` per sublayer over ``self.streams`` copies of the stream, a tanh norm (also the model's last one,
+    ``self.final_tanh_norm`` = (alpha, w, b)) and a convolution of ``self.canon_taps`` taps on every sublayer's input.
+    ``self.logit_scale`` multiplies the logits."""
 
     block_style = "sandwich"
 
@@ -728,6 +839,8 @@ class SequenceModel:
         self.lm_head: Optional[Linear] = None
         self.eps = 1e-6
         self.logit_scale = 1.0
+        self.streams, self.canon_taps = 1, 1          # "hyper" chain
+        self.final_tanh_norm: Optional[tuple] = None  # (alpha, w, b): the last norm is tanh(alpha x) w + b instead of an rms norm
         # debugging aid: callable(layer, kind, h [M, width]) run after every closed branch of an eager pass (never set it
         # while a decode step is being captured)
         self.residual_tap = None
@@ -759,6 +872,11 @@ class SequenceModel:
 
     def new_cache(self, batch_size: int) -> List[RowState]:
         """One entry per layer (its mixer's state) and a last one for the previous token of every row."""
+        if self.block_style == "hyper":
+            # per run: the mixer's state and the carried inputs of the two input convolutions
+            W, taps = self.args.width, self.canon_taps
+            return [StateGroup([r.mixer.new_state(batch_size), ConvTailState(W, taps, batch_size), ConvTailState(W, taps, batch_size)],
+                               batch_size) for r in self.runs] + [TokenState(batch_size)]
         if self.block_style in ("parallel", "prenorm"):
             return [r.mixer.new_state(batch_size) for r in self.runs] + [TokenState(batch_size)]
         return [m.new_state(batch_size) for m in self.mixers] + [TokenState(batch_size)]
@@ -791,6 +909,9 @@ class SequenceModel:
                     s.reserve("y2", torch.float32, W)
             if self.loop_in is not None:
                 s.reserve("cat", dt, 2 * W)
+            if self.block_style == "hyper":
+                s.reserve("xs", torch.float32, self.streams * W)
+                s.reserve("n", torch.float32, W)
             s.reserve("y", torch.float32, W)
             s.reserve("x", dt, W)
             s.reserve("xl", dt, W)
@@ -830,6 +951,8 @@ class SequenceModel:
             return self._chain_parallel(h, x, y, plan, s, cache, M)
         if self.block_style == "prenorm":
             return self._chain_prenorm(h, x, y, plan, s, cache)
+        if self.block_style == "hyper":
+            return self._chain_hyper(h, x, y, plan, s, cache, M)
         subs = self.sublayers
 
         def feed(nxt: Optional[Sublayer], y_in, post_w):
@@ -899,6 +1022,51 @@ class SequenceModel:
             if self.residual_tap is not None:
                 self.residual_tap(r.layer, "run", h)
 
+    def _chain_hyper(self, h, x, y, plan: dict, s: Scratch, cache: List[RowState], M: int):
+        """The runs of a "hyper" model.  h holds the embedding; the copies of the stream live in one fp32 buffer [M, streams, W].
+        Every sublayer's output is written back and the next sublayer's input read and normed in ONE pass over the copies
+        (b200p_hyper_step); the input convolution follows (prompts: b200p_canon_conv over the portion's rows and the carried
+        inputs, which b200p_delta_conv_commit then replaces; decode steps: inside the same pass).  The last pass leaves the sum of
+        the copies in h for the model's last norm."""
+        S, W, taps, dt, runs = self.streams, self.args.width, self.canon_taps, self.dtype, self.runs
+        xs, n = s.get("xs", torch.float32, M, S * W), s.get("n", torch.float32, M, W)
+        decode = plan["max_n"] == 1
+        stops = []                                     # (run, port, its carried inputs) in execution order
+        for r in runs:
+            st = cache[r.slot]
+            stops.append((r, r.port1, st.parts[1], True))
+            if r.mlp is not None:
+                stops.append((r, r.port2, st.parts[2], False))
+
+        def step(y_in, prev: Optional[StreamPort], k_next: int, want_sum: bool):
+            nxt = stops[k_next] if k_next < len(stops) else None
+            kw = dict(y=y_in, mix=prev.mix if prev else None, out=prev.out if prev else None, src=h if prev is None else None,
+                      sum_out=h if want_sum else None)
+            if nxt is None:
+                return ops.hyper_step(xs, S, **kw)
+            port, tail = nxt[1], nxt[2]
+            kw.update(read=port.read, alpha=port.alpha, w=port.w, b=port.b)
+            if decode:
+                ops.hyper_step(xs, S, conv_w=port.conv_w, conv_state=tail.conv, t_row=plan["t_row"], t_pos=plan["t_pos"], taps=taps,
+                               x_out=x, **kw)
+                return
+            ops.hyper_step(xs, S, n_out=n, **kw)
+            ops.canon_conv(n, port.conv_w, tail.conv, plan["t_row"], plan["t_pos"], plan["t_off"], x, taps)
+            if taps > 1:
+                ops.delta_conv_commit(n, tail.conv, plan["cu"], plan["rows"], plan["nb"], W, taps)
+
+        step(None, None, 0, not stops)
+        for k, (r, port, _, is_mixer) in enumerate(stops):
+            if is_mixer:
+                r.mixer(x, y, cache[r.slot].parts[0], plan, s, cache)
+            else:
+                r.mlp(x, y, s)
+            closes_run = k + 1 == len(stops) or stops[k + 1][0] is not r
+            tap = closes_run and self.residual_tap is not None
+            step(y, port, k + 1, k + 1 == len(stops) or tap)
+            if tap:
+                self.residual_tap(r.layer, "run", h)
+
     def _advance_device(self, cache: List[RowState], a: dict, B: int, ids_i32: Optional[torch.Tensor] = None):
         """End of a step on the device: lengths += tokens brought, last token of every entry remembered."""
         ops.ragged_advance(cache[-1]._lengths, cache[-1].last_token, a["ids"] if ids_i32 is None else ids_i32, a["cu"], a["rows"], B)
@@ -907,7 +1075,10 @@ class SequenceModel:
         """final norm + output projection of the given residual rows -> float32 logits."""
         n = h_rows.shape[0]
         xl = a["s"].get("xl", self.dtype, n, self.args.width)
-        ops.norm_add_norm(h_rows, self.eps, self.dtype, w_next=self.final_norm_w, x_out=xl)
+        if self.final_tanh_norm is not None:
+            ops.tanh_norm(h_rows, *self.final_tanh_norm, xl)
+        else:
+            ops.norm_add_norm(h_rows, self.eps, self.dtype, w_next=self.final_norm_w, x_out=xl)
         logits = self.lm_head(xl, GEMM_STORE_F32, out=logits_out)
         if self.logit_scale != 1.0:
             ops.scale_(logits, self.logit_scale)

@@ -113,11 +113,14 @@ class RowState:
 
 
 class BatchedKVCache(RowState):
-    def __init__(self, head_dim, n_kv_heads, batch_size=1, value_dim=None):
+    def __init__(self, head_dim, n_kv_heads, batch_size=1, value_dim=None, values_are_keys=False):
         super().__init__(batch_size)
         self.n_kv_heads = n_kv_heads
         self.head_dim = head_dim
         self.value_dim = head_dim if value_dim is None else value_dim     # designs whose values are not the keys' size
+        self.values_are_keys = bool(values_are_keys)                      # designs that attend over their keys: one buffer
+        if self.values_are_keys and self.value_dim != head_dim:
+            raise ValueError("values that are the keys have the keys' size")
         self.keys: Optional[torch.Tensor] = None
         self.values: Optional[torch.Tensor] = None
 
@@ -162,12 +165,14 @@ class BatchedKVCache(RowState):
             # base.py:104-117).  Only ONE layer's old + new buffers are alive at a time.
             new_cap = max(new_cap, ((cap * 3 // 2 + self.step - 1) // self.step) * self.step)
         nk = torch.zeros((self.batch_size, self.n_kv_heads, new_cap, self.head_dim), dtype=dtype, device=device)
-        nv = torch.zeros((self.batch_size, self.n_kv_heads, new_cap, self.value_dim), dtype=dtype, device=device)
+        nv = nk if self.values_are_keys else torch.zeros((self.batch_size, self.n_kv_heads, new_cap, self.value_dim), dtype=dtype,
+                                                          device=device)
         if self.keys is not None and cap > 0:
             keep = min(cap, max(self._offsets) if self._offsets else 0)
             if keep > 0:
                 nk[:, :, :keep] = self.keys[:, :, :keep]
-                nv[:, :, :keep] = self.values[:, :, :keep]
+                if not self.values_are_keys:
+                    nv[:, :, :keep] = self.values[:, :, :keep]
         self.keys, self.values = nk, nv
         return True
 
@@ -233,6 +238,22 @@ class DeltaRuleState(RowState):
         return True
 
 
+class ConvTailState(RowState):
+    """The last ``taps - 1`` inputs of a causal convolution over time, ``conv [B, taps-1, C]`` (fp32): what a layer that
+    convolves its input (or its projections) carries from step to step.  Constant size per row; never grows."""
+    def __init__(self, channels, taps, batch_size=1):
+        super().__init__(batch_size)
+        self.channels, self.taps = channels, taps
+        self.conv: Optional[torch.Tensor] = None
+    def _drop_buffers(self):
+        self.conv = None
+    def buffers(self) -> tuple:
+        return (self.conv,)
+    def ensure_capacity(self, needed: int, dtype, device) -> bool:
+        if self.conv is not None:
+            return False
+        self.conv = torch.zeros((self.batch_size, max(self.taps - 1, 1), self.channels), dtype=torch.float32, device=device)
+        return True
 class StateGroup(RowState):
     """The states of a layer whose mixer is several mixers side by side (say a KV cache and a matrix state): one entry of the
     cache list that owns its parts' buffers.  The parts keep no bookkeeping of their own; they follow this entry's rows."""

@@ -567,3 +567,108 @@ def latent_attn(q, cache, t_row, t_pos, out, H, R, window, scale, cu=None, rows=
     _call("b200p_latent_attn", lambda: lib().b200p_latent_attn(_p(q), _p(cache), cache.shape[1], _p(t_row), _p(t_pos), _p(out), M, H, R,
                                                               int(window), float(scale), dtype_code(cache.dtype), _stream()))
     return out
+
+
+def latent_rope_prep(proj, q_rank, kv_rank, rot_dim, wq, wkv, eps, rates, mag, cq_out, cache, t_row, t_pos):
+    """Latent attention with a rotated key part: ``proj`` = [query | key/value | rotated part]; ``cache`` [rows, Tcap, row] gets
+    [normed latent | rotated part | zeros]."""
+    _dev(proj, wq, wkv, rates, cq_out, cache, t_row, t_pos)
+    M = proj.shape[0]
+    assert proj.dtype == torch.float32 and cache.is_contiguous() and cq_out.is_contiguous() and cq_out.dtype == cache.dtype
+    _call("b200p_latent_rope_prep", lambda: lib().b200p_latent_rope_prep(
+        _p(proj), proj.stride(0), int(q_rank), int(kv_rank), int(rot_dim), cache.shape[2], _p(wq), _p(wkv), float(eps), _p(rates), float(mag),
+        _p(cq_out), _p(cache), cache.shape[1], _p(t_row), _p(t_pos), M, dtype_code(cache.dtype), _stream()))
+
+
+def latent_q_rope(q, H, dim, rot_dim, kv_rank, rates, mag, t_pos, q_lat):
+    """The rotated part of the queries ``q`` [M, H * (dim + rot_dim)] into columns [kv_rank, kv_rank + rot_dim) of every head's
+    row of ``q_lat`` fp32 [M, H * row]; the columns behind become zero."""
+    _dev(q, rates, t_pos, q_lat)
+    M = q.shape[0]
+    row = q_lat.shape[1] // H
+    assert q.is_contiguous() and q_lat.is_contiguous() and q_lat.dtype == torch.float32 and q.shape[1] == H * (dim + rot_dim)
+    _call("b200p_latent_q_rope", lambda: lib().b200p_latent_q_rope(_p(q), H, int(dim), int(rot_dim), int(kv_rank), row, _p(rates), float(mag),
+                                                                  _p(t_pos), _p(q_lat), M, dtype_code(q.dtype), _stream()))
+
+
+def window_attn_prep(proj, col_q, conv_w, conv_state, taps, scale, q_out, kcache, t_row, t_pos, t_off, H, G, dk):
+    """Convolved q (scaled, fp32) to ``q_out``; convolved k into ``kcache`` [rows, G, Tcap, dk] at every token's (row, position)."""
+    _dev(proj, conv_w, conv_state, q_out, kcache, t_row, t_pos, t_off)
+    M = proj.shape[0]
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and kcache.is_contiguous() and q_out.is_contiguous()
+    assert kcache.shape[1:] == (G, kcache.shape[2], dk) and conv_w.shape == ((H + G) * dk, taps)
+    _call("b200p_window_attn_prep", lambda: lib().b200p_window_attn_prep(
+        _p(proj), proj.stride(0), int(col_q), _p(conv_w), _p(conv_state), int(taps), float(scale), _p(q_out), _p(kcache), kcache.shape[2],
+        _p(t_row), _p(t_pos), _p(t_off), M, H, G, dk, dtype_code(kcache.dtype), _stream()))
+
+
+def window_attn(q, kcache, vcache, t_row, t_pos, out, H, G, dk, dv, softcap=0.0, r1=None, r2=None, window=0, gate=None, cu=None,
+                rows=None, nb=0, max_n=1, workspace=None):
+    """Sliding-window attention with capped scores, a logarithmic distance penalty and an output gate (every option off at its
+    default); ``vcache`` may be ``kcache``.  ``gate``: fp32 [M, >= H * dv] pre-activations (a column slice is fine)."""
+    _dev(q, kcache, vcache, t_row, t_pos, out, r1, r2, gate, cu, rows)
+    M = q.shape[0]
+    assert q.dtype == torch.float32 and q.is_contiguous() and out.stride(1) == 1 and out.dtype == kcache.dtype
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1)
+    _call("b200p_window_attn", lambda: lib().b200p_window_attn(
+        _p(q), _p(kcache), _p(vcache), kcache.shape[2], _p(t_row), _p(t_pos), _p(cu), _p(rows), int(nb), int(max_n), float(softcap), _p(r1),
+        _p(r2), int(window), _p(gate), 0 if gate is None else gate.stride(0), _p(out), out.stride(0), M, H, G, dk, dv,
+        dtype_code(kcache.dtype), _p(workspace), 0 if workspace is None else workspace.numel() * 4, _stream()))
+    return out
+
+
+def moe_route_scores(logits, ids, wts, seg, slot_of, token_of, top: int, experts: Optional[int] = None):
+    """Routing by the largest sigmoid scores; the weights are the scores themselves."""
+    _dev(logits, ids, wts, seg, slot_of, token_of)
+    M = logits.shape[0]
+    E = logits.shape[1] if experts is None else int(experts)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    _call("b200p_moe_route_scores", lambda: lib().b200p_moe_route_scores(_p(logits), logits.stride(0), _p(ids), _p(wts), _p(seg), _p(slot_of),
+                                                                        _p(token_of), M, E, int(top), _stream()))
+
+
+def moe_scatter_scaled(x, slot_of, wts, xs, top: int):
+    """xs[slot of (t, k)] = wts[t, k] * x[t]: the routing weight on the expert's input."""
+    _dev(x, slot_of, wts, xs)
+    assert x.is_contiguous() and xs.is_contiguous() and x.dtype == xs.dtype and x.shape[1] == xs.shape[1] and wts.dtype == torch.float32
+    _call("b200p_moe_scatter_scaled", lambda: lib().b200p_moe_scatter_scaled(_p(x), _p(slot_of), _p(wts), _p(xs), x.shape[0], x.shape[1],
+                                                                            int(top), dtype_code(x.dtype), _stream()))
+
+
+def hyper_step(xs, streams: int, y=None, src=None, mix=None, out=None, read=None, alpha=None, w=None, b=None, n_out=None, sum_out=None,
+               conv_w=None, conv_state=None, t_row=None, t_pos=None, taps=1, x_out=None):
+    """One pass over the copies of the residual stream ``xs`` fp32 [M, streams * W]: write a sublayer's output ``y`` back
+    (``mix`` [from, to], ``out``), read for the next one (``read``) and norm it with tanh(alpha u) w + b into ``n_out``; with
+    ``x_out`` (a decode step) the short convolution over the carried inputs is added and the carried inputs are shifted too."""
+    _dev(xs, y, src, mix, out, read, alpha, w, b, n_out, sum_out, conv_w, conv_state, t_row, t_pos, x_out)
+    M = xs.shape[0]
+    W = xs.shape[1] // streams
+    assert xs.dtype == torch.float32 and xs.is_contiguous()
+    for t in (y, src, n_out, sum_out):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.shape == (M, W))
+    for t in (mix, out, read, alpha, w, b, conv_w):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous())
+    assert (mix is None) == (out is None) and (mix is None or mix.numel() == streams * streams)
+    assert x_out is None or (x_out.is_contiguous() and conv_w.shape == (W, taps) and conv_state.is_contiguous())
+    _call("b200p_hyper_step", lambda: lib().b200p_hyper_step(
+        _p(xs), _p(y), _p(src), _p(mix), _p(out), _p(read), _p(alpha), _p(w), _p(b), _p(n_out), _p(sum_out), M, int(streams), W, _p(conv_w),
+        _p(conv_state), _p(t_row), _p(t_pos), int(taps), _p(x_out), dtype_code(x_out.dtype if x_out is not None else torch.float32),
+        _stream()))
+
+
+def canon_conv(n, conv_w, conv_state, t_row, t_pos, t_off, x_out, taps: int):
+    """x_out = n + causal convolution of n over time (``conv_w`` [W, taps]; ``conv_state`` [rows, taps-1, W] = earlier steps)."""
+    _dev(n, conv_w, conv_state, t_row, t_pos, t_off, x_out)
+    M, W = n.shape
+    assert n.dtype == torch.float32 and n.is_contiguous() and x_out.is_contiguous() and conv_w.shape == (W, taps) and conv_state.is_contiguous()
+    _call("b200p_canon_conv", lambda: lib().b200p_canon_conv(_p(n), _p(conv_w), _p(conv_state), _p(t_row), _p(t_pos), _p(t_off), _p(x_out), M,
+                                                            W, int(taps), dtype_code(x_out.dtype), _stream()))
+
+
+def tanh_norm(h, alpha, w, b, x_out):
+    """x_out = tanh(alpha h) w + b, rows of fp32 ``h`` into the storage type."""
+    _dev(h, alpha, w, b, x_out)
+    M, W = h.shape
+    assert h.dtype == torch.float32 and h.is_contiguous() and x_out.is_contiguous()
+    _call("b200p_tanh_norm", lambda: lib().b200p_tanh_norm(_p(h), _p(alpha), _p(w), _p(b), _p(x_out), M, W, dtype_code(x_out.dtype),
+                                                          _stream()))
