@@ -221,3 +221,127 @@ def forward(cfg, P, tokens, tap=None, chosen=None):
         if tap is not None:
             tap(i, xs.sum(0))
     return tanh_norm(xs.sum(0), P, "final.norm") @ P["embed"].T
+
+
+# ---- small configurations and random weights for the tests ------------------------------------------------------------------
+def moe_mlp(experts, top, ff, limit=1.0):
+    return {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": {"experts": experts, "top": top}}
+
+
+def delta_layer(heads, kv_heads, dim, vdim, conv, mlp=None):
+    return {"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv}, "mlp": mlp}
+
+
+def latent_layer(heads, dim, rot_dim, vdim, q_rank, kv_rank, scale, base=10000.0, scaling=None, mlp=None):
+    rot = {"dims": rot_dim, "base": base}
+    if scaling:
+        rot["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
+    return {"type": "latent_attention", "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "q_rank": q_rank,
+                                                  "kv_rank": kv_rank, "scale": scale, "rot": rot}, "mlp": mlp}
+
+
+def window_layer(heads, kv_heads, dim, scale, window, softcap, conv, mlp=None):
+    return {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": scale, "softcap": softcap,
+                                           "mask": {"size": window}, "conv": conv}, "mlp": mlp}
+
+
+def make_config(layers, vocab=40, width=32, eps=1e-5, streams=2, taps=3):
+    return {"architecture": "Dapupel", "vocab": vocab, "width": width, "layers": layers, "norm": {"eps": eps}, "streams": streams,
+            "canon": {"taps": taps}}
+
+
+def low_rank(width):
+    """inner sizes of the decay's and the gate's pairs of matrices (the config does not give them: the tensors do)"""
+    return max(4, width // 8), max(4, width // 8 + 3)
+
+
+def shapes(cfg):
+    W, V, S, taps = cfg["width"], cfg["vocab"], cfg["streams"], cfg["canon"]["taps"]
+    s = {"embed": (V, W), "final.norm": (W,), "final.norm.b": (W,), "final.norm.alpha": ()}
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        for q in ("1", "2") if L.get("mlp") is not None else ("1",):
+            s.update({f"{p}norm{q}": (W,), f"{p}norm{q}.b": (W,), f"{p}norm{q}.alpha": (), f"{p}hc{q}.in": (S,), f"{p}hc{q}.out": (S,),
+                      f"{p}hc{q}.mix": (S, S), f"{p}canon{q}": (W, taps)})
+        if L["type"] == "channel_delta":
+            ck, cv, n = m["kv_heads"] * m["dim"], m["heads"] * m["vdim"], m["conv"]
+            ra, rg = low_rank(W)
+            s.update({p + "mix.q": (ck, W), p + "mix.q.conv": (ck, n), p + "mix.k": (ck, W), p + "mix.k.conv": (ck, n), p + "mix.v": (cv, W),
+                      p + "mix.v.conv": (cv, n), p + "mix.b": (m["heads"], W), p + "mix.A_log": (m["heads"],), p + "mix.norm": (m["vdim"],),
+                      p + "mix.a1": (ra, W), p + "mix.a2": (m["heads"] * m["dim"], ra), p + "mix.dt_bias": (m["heads"] * m["dim"],),
+                      p + "mix.g1": (rg, W), p + "mix.g2": (cv, rg), p + "mix.o": (W, cv)})
+        elif L["type"] == "latent_attention":
+            H = m["heads"]
+            s.update({p + "mix.dq": (m["q_rank"], W), p + "mix.dq.norm": (m["q_rank"],), p + "mix.uq": (H * (m["dim"] + m["rot_dim"]), m["q_rank"]),
+                      p + "mix.dkv": (m["kv_rank"] + m["rot_dim"], W), p + "mix.dkv.norm": (m["kv_rank"],),
+                      p + "mix.uk": (H * m["dim"], m["kv_rank"]), p + "mix.uv": (H * m["vdim"], m["kv_rank"]), p + "mix.o": (W, H * m["vdim"])})
+        else:
+            cq, ck, n = m["heads"] * m["dim"], m["kv_heads"] * m["dim"], m["conv"]
+            s.update({p + "mix.q": (cq, W), p + "mix.k": (ck, W), p + "mix.q.conv": (cq, n), p + "mix.k.conv": (ck, n), p + "mix.r1": (m["heads"],),
+                      p + "mix.r2": (m["heads"],), p + "mix.g": (cq, W), p + "mix.o": (W, cq)})
+        mlp = L.get("mlp")
+        if mlp is None:
+            continue
+        E, ff = mlp["router"]["experts"], mlp["expert"]["ff"]
+        for e in range(E):
+            s.update({f"{p}mlp.e{e}.gate": (ff, W), f"{p}mlp.e{e}.up": (ff, W), f"{p}mlp.e{e}.down": (W, ff)})
+        s[p + "mlp.router"] = (E, W)
+    return s
+
+
+def random_weights(cfg, seed=0, dtype=torch.float32, gain=1.0):
+    """Random tensors of every shape, scaled so that each branch moves the stream visibly (``gain`` multiplies the projection
+    matrices: below one, a rounding error early in the model grows less on its way to the logits); values are rounded to
+    bfloat16 (kept in ``dtype``) so that a bfloat16 model holds the same numbers."""
+    g = torch.Generator().manual_seed(seed)
+    S = cfg["streams"]
+    P = {}
+    for name, shape in shapes(cfg).items():
+        parts = name.split(".")
+        leaf = parts[-1]
+        if leaf == "alpha":
+            t = torch.rand(shape, generator=g) * 0.6 + 0.5
+        elif len(parts) >= 2 and parts[-2].startswith("hc"):
+            if leaf == "mix":
+                t = torch.eye(S) * 0.8 + torch.randn(shape, generator=g) * 0.25
+            elif leaf == "in":
+                t = torch.rand(shape, generator=g) * 0.8 + 0.3
+            else:
+                t = torch.randn(shape, generator=g) * 0.4 + 0.8
+        elif leaf.startswith("canon"):
+            t = torch.randn(shape, generator=g) * 0.4
+        elif leaf == "conv":
+            t = torch.randn(shape, generator=g) * 0.5
+            if "q" in parts or "k" in parts:
+                t[:, -1] += 1.0
+        elif leaf in ("r1", "r2"):
+            t = torch.rand(shape, generator=g) * 0.8 + 0.1
+        elif leaf == "b" and parts[-2].startswith("norm"):
+            t = torch.randn(shape, generator=g) * 0.2
+        elif leaf in ("norm1", "norm2") or name == "final.norm":
+            t = 1.0 + torch.randn(shape, generator=g) * 0.3
+        elif leaf == "norm":
+            t = 1.0 + torch.randn(shape, generator=g) * 0.2
+        elif leaf == "A_log":
+            t = torch.rand(shape, generator=g) * 1.5 - 1.0
+        elif leaf == "dt_bias":
+            t = torch.randn(shape, generator=g) * 0.7 - 0.5
+        elif name == "embed":
+            t = torch.randn(shape, generator=g) * 0.8
+        elif len(shape) == 2:
+            t = torch.randn(shape, generator=g) * (1.5 * gain / math.sqrt(shape[1]))
+            if leaf == "router":
+                t = t * 2.0
+        else:
+            raise KeyError(name)
+        P[name] = t.to(torch.bfloat16).to(dtype)
+    return P
+
+
+def logits_error(got, want):
+    """Worst position: rms over the vocabulary of the centred difference, relative to the rms of the centred expected row."""
+    got, want = got.to(F64).cpu(), want.to(F64).cpu()
+    d = got - want
+    d = d - d.mean(-1, keepdim=True)
+    w = want - want.mean(-1, keepdim=True)
+    return float((d.pow(2).mean(-1).sqrt() / w.pow(2).mean(-1).sqrt().clamp_min(1e-30)).max())
