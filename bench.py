@@ -479,15 +479,16 @@ def _gemm_rooflines(prof, rows, w_bytes_per_el, tflops, hbm_gbs):
 def design_compare(design, sizes, steps, warmup, B_prefill=4, L_prefill=2048, B_decode=32, T_ctx=1024):
     """Prefill and decode throughput of the design at layer sizes of real models (random weights, few layers), beside the
     closest existing graph of this framework at equal width / feed-forward / head count: for Dogulorn the Llama graph (4-bit
-    weights, its usual format), for Pupopel the Dogulorn graph and for Nifalorn the Pupopel graph (dense bf16 weights, the same
-    ragged engine)."""
+    weights, its usual format), for Pupopel the Dogulorn graph, for Nifalorn and Dapupel the Pupopel graph (dense bf16 weights,
+    the same ragged engine)."""
     import torch
     from mlx_parallm_b200 import _lib, ops, synth
     from mlx_parallm_b200.utils import DecodeSession, _get_classes
     makers = {"dogulorn": (synth.dogulorn_config, synth.dogulorn_random_weights),
               "pupopel": (synth.pupopel_config, synth.pupopel_random_weights),
-              "nifalorn": (synth.nifalorn_config, synth.nifalorn_random_weights)}
-    closest = {"pupopel": "dogulorn", "nifalorn": "pupopel"}        # the reference graph on the same engine (Dogulorn: Llama, below)
+              "nifalorn": (synth.nifalorn_config, synth.nifalorn_random_weights),
+              "dapupel": (synth.dapupel_config, synth.dapupel_random_weights)}
+    closest = {"pupopel": "dogulorn", "nifalorn": "pupopel", "dapupel": "pupopel"}        # the reference graph on the same engine (Dogulorn: Llama, below)
     assert design in makers
     _lib.require_device()
     hbm, src = peaks()
@@ -629,7 +630,7 @@ def main():
     ap.add_argument("--sweep", default=",".join(DEFAULT_SWEEP), help="comma list of extra workloads ('' = none)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
-    ap.add_argument("--design", default=None, choices=["dogulorn", "pupopel", "nifalorn"],
+    ap.add_argument("--design", default=None, choices=["dogulorn", "pupopel", "nifalorn", "dapupel"],
                     help="instead of the headline workload: prefill / decode throughput of this design at real layer sizes, "
                          "beside the closest existing graph at equal size (one JSON line of its own shape)")
     ap.add_argument("--design-sizes", default=",".join(DESIGN_SIZES))

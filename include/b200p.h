@@ -494,7 +494,7 @@ int b200p_latent_q_rope(const void* q, int H, int dim, int rot_dim, int kv_rank,
                         const int32_t* t_pos, float* q_lat, int64_t M, int dtype, void* stream);
 
 /* Windowed attention with capped scores for designs without rotation.  Step 1: proj fp32 [M, ldp] holds q (H x dk) | k (G x dk)
- * from column col_q; both pass a causal convolution over time (conv_w [(H + G) dk, taps], the last tap the current token's;
+ * from column col_q; both pass a causal convolution over time (conv_w [taps, (H + G) dk], tap by tap, the last tap the current token's;
  * conv_state [rows, taps-1, (H + G) dk] carries the inputs of earlier steps: commit it afterwards with b200p_delta_conv_commit on the
  * same columns; taps == 1: one factor per channel).  q_out fp32 [M, H dk] = that * scale; the keys go to kcache [rows, G, Tcap, dk]. */
 int b200p_window_attn_prep(const float* proj, int64_t ldp, int64_t col_q, const float* conv_w, const float* conv_state, int taps,
@@ -516,7 +516,8 @@ int b200p_window_attn(const float* q, const void* kcache, const void* vcache, in
  *   sum_out [M, W] (or NULL) = sum_r x'_r
  *   u = sum_r in[r] x'_r;  n = tanh(alpha[0] u) w + b  (w NULL: n = u; b NULL: no offset);  n_out [M, W] (or NULL) = n
  * With x_out (dtype [M, W]) the step is a decode step, one token per entry, and the pass also adds the causal convolution over time
- * of n: x = n + sum_j conv_w[:, j] n_(t - taps + 1 + j) from conv_state [rows, taps-1, W] (inputs before position 0 count as zero),
+ * of n: x = n + sum_j conv_w[j, :] n_(t - taps + 1 + j) (conv_w fp32 [taps, W], tap by tap) from conv_state [rows, taps-1, W] (inputs
+ * before position 0 count as zero),
  * then shifts n into conv_state.  streams <= 8, taps <= 16. */
 int b200p_hyper_step(float* xs, const float* y, const float* src, const float* mix, const float* out, const float* in,
                      const float* alpha, const float* w, const float* b, float* n_out, float* sum_out, int64_t M, int streams,

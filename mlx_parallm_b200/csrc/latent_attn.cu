@@ -184,11 +184,12 @@ latent_attn_kernel(const float* __restrict__ q, const T* __restrict__ cache, int
 //   P   8 threads per row: running max / sum in fp32, p = exp(s - max) as 16-bit       -> shared P [16, 64]
 //   O   warp w: columns [w R/4, (w+1) R/4) of o [16, R] += P x c[64 keys, its columns]   (accumulators rescaled first)
 constexpr int LT_ROWS = 16, LT_KEYS = 64, LT_THREADS = 128, LT_MAX_NT = 16;      // R <= 512, R % 32 == 0
+constexpr int LT_WIDE_NT = 20;     // a second instantiation with more accumulators: 512 < R <= 640 (a 512-value latent plus a rotated part)
 constexpr int LT_MAX_GROUPS = 4;
 
 int sm_count();
 
-template <typename T, int G>
+template <typename T, int G, int MAXNT>
 __global__ void __launch_bounds__(LT_THREADS * G)
 latent_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ cache, int64_t Tcap, const int32_t* __restrict__ cu,
                         const int32_t* __restrict__ rows, const int32_t* __restrict__ t_pos, T* __restrict__ out, int H, int R,
@@ -230,9 +231,9 @@ latent_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ cache
   }
   if (tl < LT_ROWS) { row_m[tl] = -INFINITY; row_l[tl] = 0.f; }
   const int ntw = R / 32;                                        // 8-column tiles of o per warp
-  float o[LT_MAX_NT][4];
+  float o[MAXNT][4];
 #pragma unroll
-  for (int i = 0; i < LT_MAX_NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  for (int i = 0; i < MAXNT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   const int chunks_per_row = R / 8;
   int64_t jbeg = kmin, jend = plast;                             // this CTA's keys, inclusive
   if (splits > 1) {
@@ -317,13 +318,13 @@ latent_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ cache
     if (active) {   // ---- O
       const float c0 = row_c[lane >> 2], c1 = row_c[(lane >> 2) + 8];
 #pragma unroll
-      for (int i = 0; i < LT_MAX_NT; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
+      for (int i = 0; i < MAXNT; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
 #pragma unroll
       for (int kk = 0; kk < LT_KEYS; kk += 16) {
         uint32_t a[4];
         ldsm_x4((uint32_t)__cvta_generic_to_shared(ps + (lane & 15) * 72 + kk + (lane >> 4) * 8), a);
 #pragma unroll
-        for (int jp = 0; jp < LT_MAX_NT / 2; ++jp) {
+        for (int jp = 0; jp < MAXNT / 2; ++jp) {
           if (2 * jp < ntw) {
             uint32_t b[4];
             ldsm_x4_trans((uint32_t)__cvta_generic_to_shared(cs + (kk + (lane & 15)) * LDC + warp * (R / 4) + jp * 16 + (lane >> 4) * 8), b);
@@ -340,7 +341,7 @@ latent_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ cache
     cg::cluster_group cluster = cg::this_cluster();
     float* po = reinterpret_cast<float*>(cs0);                    // [16][R] unnormalised partial sums (the chunk buffer is free now)
 #pragma unroll
-    for (int i = 0; i < LT_MAX_NT; ++i) {
+    for (int i = 0; i < MAXNT; ++i) {
       if (i < ntw) {
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
@@ -389,7 +390,7 @@ latent_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ cache
     return;
   }
 #pragma unroll
-  for (int i = 0; i < LT_MAX_NT; ++i) {
+  for (int i = 0; i < MAXNT; ++i) {
     if (i < ntw) {
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
@@ -480,7 +481,7 @@ static int g_lt_groups = 0;     // 0: chosen per launch; 1..4: forced (b200p_lat
 static int g_lt_nbuf = 0;       // chunk buffers of the tile kernel: 0 = chosen per launch, 1 or 2 forced (b200p_latent_attn_set_buffers)
 static int g_lt_splits = 0;     // decode: 0 = chosen per launch; 1 = one CTA per tile; 2, 4, 8 = forced (b200p_latent_attn_set_splits)
 
-template <typename T>
+template <typename T, int MAXNT>
 static int latent_attn_tile_launch(const float* q, const void* cache, int64_t Tcap, const int32_t* cu, const int32_t* rows,
                                    const int32_t* t_pos, void* out, int nb, int max_n, int H, int R, int64_t window, float scale,
                                    cudaStream_t st) {
@@ -488,7 +489,8 @@ static int latent_attn_tile_launch(const float* q, const void* cache, int64_t Tc
   const int units = by_head ? (H + LT_ROWS - 1) / LT_ROWS : H;                   // 16-row tiles that share one set of keys
   // Two tiles per CTA halve the L2 -> shared traffic per head and win on prompts from rank 128 up (1.1x at rank 256, 1.8x at
   // rank 512); four leave one CTA per SM (registers) and lose the overlap between CTAs again.  Decode steps gain nothing.
-  int G = g_lt_groups > 0 ? g_lt_groups : (by_head || R < 128) ? 1 : 2;
+  // Above rank 512 one CTA per SM is all that fits: four tiles on one staged copy then beat two (5.7 -> 4.3 ms at rank 576).
+  int G = g_lt_groups > 0 ? g_lt_groups : (by_head || R < 128) ? 1 : R > 32 * LT_MAX_NT ? 4 : 2;
   if (G > units) G = units;
   if (G == 3) G = 2;
   const size_t group_bytes = ((size_t)LT_ROWS * (R + 8) + LT_ROWS * 72) * sizeof(T) + (LT_ROWS * 68 + 3 * LT_ROWS) * sizeof(float);
@@ -497,7 +499,7 @@ static int latent_attn_tile_launch(const float* q, const void* cache, int64_t Tc
   const size_t chunk_bytes = (size_t)LT_KEYS * (R + 8) * sizeof(T);
   const int nbuf = g_lt_nbuf > 0 ? g_lt_nbuf : 2 * (2 * chunk_bytes + G * group_bytes) <= 220 * 1024 ? 2 : 1;
   const size_t smem = nbuf * chunk_bytes + G * group_bytes;
-  auto kern = G == 1 ? latent_attn_tile_kernel<T, 1> : G == 2 ? latent_attn_tile_kernel<T, 2> : latent_attn_tile_kernel<T, 4>;
+  auto kern = G == 1 ? latent_attn_tile_kernel<T, 1, MAXNT> : G == 2 ? latent_attn_tile_kernel<T, 2, MAXNT> : latent_attn_tile_kernel<T, 4, MAXNT>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(latent_attn_tile_kernel)");
@@ -551,17 +553,21 @@ extern "C" int b200p_latent_attn_set_splits(int splits) {
 }
 
 extern "C" int b200p_latent_attn_tiles_supported(int R, int dtype) {
-  return (dtype == B200P_F16 || dtype == B200P_BF16) && R % 32 == 0 && R <= 32 * LT_MAX_NT ? 1 : 0;
+  return (dtype == B200P_F16 || dtype == B200P_BF16) && R % 32 == 0 && R <= 32 * LT_WIDE_NT ? 1 : 0;
 }
 
 extern "C" int b200p_latent_attn_tiles(const float* q, const void* cache, int64_t Tcap, const int32_t* cu, const int32_t* rows,
                                        const int32_t* t_pos, void* out, int nb, int max_n, int H, int R, int64_t window,
                                        float scale, int dtype, void* stream) {
   B200P_REQUIRE(q && cache && cu && rows && t_pos && out, B200P_ERR_ARG, "null pointer");
-  B200P_REQUIRE(b200p_latent_attn_tiles_supported(R, dtype), B200P_ERR_ARG, "the tile kernel needs a 16-bit type and a rank that is a multiple of 32, at most %d", 32 * LT_MAX_NT);
+  B200P_REQUIRE(b200p_latent_attn_tiles_supported(R, dtype), B200P_ERR_ARG, "the tile kernel needs a 16-bit type and a rank that is a multiple of 32, at most %d", 32 * LT_WIDE_NT);
   B200P_REQUIRE(nb > 0 && nb < 65536 && H > 0 && H < 65536 && max_n > 0, B200P_ERR_ARG, "bad batch geometry");
   B200P_REQUIRE(aligned(cache, 16) && aligned(q, 16) && aligned(out, 4), B200P_ERR_ALIGN, "cache and q must be 16-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == B200P_F16) return latent_attn_tile_launch<__half>(q, cache, Tcap, cu, rows, t_pos, out, nb, max_n, H, R, window, scale, st);
-  return latent_attn_tile_launch<__nv_bfloat16>(q, cache, Tcap, cu, rows, t_pos, out, nb, max_n, H, R, window, scale, st);
+  if (R > 32 * LT_MAX_NT) {
+    if (dtype == B200P_F16) return latent_attn_tile_launch<__half, LT_WIDE_NT>(q, cache, Tcap, cu, rows, t_pos, out, nb, max_n, H, R, window, scale, st);
+    return latent_attn_tile_launch<__nv_bfloat16, LT_WIDE_NT>(q, cache, Tcap, cu, rows, t_pos, out, nb, max_n, H, R, window, scale, st);
+  }
+  if (dtype == B200P_F16) return latent_attn_tile_launch<__half, LT_MAX_NT>(q, cache, Tcap, cu, rows, t_pos, out, nb, max_n, H, R, window, scale, st);
+  return latent_attn_tile_launch<__nv_bfloat16, LT_MAX_NT>(q, cache, Tcap, cu, rows, t_pos, out, nb, max_n, H, R, window, scale, st);
 }

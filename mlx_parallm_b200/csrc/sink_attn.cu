@@ -28,6 +28,7 @@ struct ScoreRule {
   int window;           // > 0: only keys with 0 <= p - j < window are seen
   const float* gate;    // fp32 [M, ldg]: out[t, h, c] *= sigmoid(gate[t, h dv + c]); NULL: none
   int64_t ldg;
+  int table;            // prompts on the tile kernel: entries of the per-CTA penalty table in shared memory (0: computed per score)
 };
 
 __device__ __forceinline__ float ruled_score(float s, const ScoreRule& rule, float r1, float r2, float dist) {
@@ -36,6 +37,17 @@ __device__ __forceinline__ float ruled_score(float s, const ScoreRule& rule, flo
   return s;
 }
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+// The same rule on the special-function unit, for the 16-bit tile kernel whose probabilities are rounded to 16 bits anyway:
+// tanh x = 1 - 2 / (1 + e^2x) (absolute error near 1e-7, so cap tanh(s / cap) is off by about cap * 1e-7), ln through lg2.
+// The penalty of a distance comes from `tab` (filled once per CTA: a prompt tile serves one head) where there is one.
+__device__ __forceinline__ float ruled_score_fast(float s, const ScoreRule& rule, float two_inv_cap, float r1, float r2, int dist,
+                                                  const float* tab) {
+  if (rule.cap > 0.f) s = rule.cap * (1.f - __fdividef(2.f, 1.f + __expf(s * two_inv_cap)));
+  if (tab) s -= tab[dist];
+  else if (rule.r1) s -= r1 * __logf(fmaf(r2, (float)dist, 1.f));
+  return s;
+}
+__device__ __forceinline__ float sigmoid_fast(float z) { return __fdividef(1.f, 1.f + __expf(-z)); }
 
 // slope of head h: 2^(slope_log2 * (h + 1) / H); slope_log2 = 0 means no bias
 __device__ __forceinline__ float head_slope(float slope_log2, int h, int H) {
@@ -166,7 +178,7 @@ sink_attn_kernel(const float* __restrict__ q, const T* __restrict__ kcache, cons
 }
 
 // q and k of the windowed attention: projections [q (H dk) | k (G dk)] from column col_q of proj pass a causal convolution over
-// time (conv_w [C, taps], last tap the current token's; conv_state [rows, taps-1, C] the inputs of earlier steps, zeros before the
+// time (conv_w [taps, C], tap by tap, the last tap the current token's; conv_state [rows, taps-1, C] the inputs of earlier steps, zeros before the
 // sequence's start); q_out = that * scale (fp32), the keys go to the cache.
 template <typename T>
 __global__ void window_attn_prep_kernel(const float* __restrict__ proj, int64_t ldp, int64_t col_q, const float* __restrict__ conv_w,
@@ -185,7 +197,7 @@ __global__ void window_attn_prep_kernel(const float* __restrict__ proj, int64_t 
       if (d > pos) in = 0.f;
       else if (d <= off) in = pt[c - (int64_t)d * ldp];
       else in = conv_state[((int64_t)row * (taps - 1) + (taps - 1 + off - d)) * C + c];
-      acc = fmaf(conv_w[(int64_t)c * taps + j], in, acc);
+      acc = fmaf(conv_w[(int64_t)j * C + c], in, acc);
     }
     if (c < Cq) q_out[t * Cq + c] = acc * scale;
     else if (pos < Tcap) {                           // the host sizes the cache first; never write outside it
@@ -250,6 +262,14 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
   }
   float r1_0 = 0.f, r2_0 = 0.f, r1_1 = 0.f, r2_1 = 0.f;
   if (RULED && rule.r1) { r1_0 = rule.r1[h0]; r2_0 = rule.r2[h0]; r1_1 = rule.r1[h1]; r2_1 = rule.r2[h1]; }
+  const float two_inv_cap = (RULED && rule.cap > 0.f) ? 2.f / rule.cap : 0.f;
+  const float* ptab = nullptr;
+  if (RULED && !DECODE && rule.r1 && rule.table > 0) {
+    // every distance a visible pair of this CTA can have (below the window) once, instead of a logarithm per score
+    float* tab = reinterpret_cast<float*>(st_smem + ST_STAGES * (ST_KT * (DK + DV) * 2));
+    for (int i = threadIdx.x; i < rule.table; i += NT) tab[i] = r1_0 * __logf(fmaf(r2_0, (float)i, 1.f));
+    ptab = tab;                                                     // read after the first tile's __syncthreads
+  }
   const float slope2_0 = head_slope(slope_log2, h0, H) * LOG2E, slope2_1 = head_slope(slope_log2, h1, H) * LOG2E;
 
   uint32_t qf[DK / 16][4];
@@ -270,6 +290,8 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
   const int64_t row = rows[e];
   const T* kbase = kc + (row * G + g) * Tcap * DK;
   const T* vbase = vc + (row * G + g) * Tcap * DV;
+  // values that are the keys (one buffer, equal sizes): the staged key tile serves both products and no value tile is loaded
+  const bool same_kv = RULED && DK == DV && kc == vc;
   auto issue_tile = [&](int tile, int stage) {
     const uint32_t ks = sbase + stage * STAGE_BYTES, vs = ks + K_BYTES;
     const int key0 = tile * ST_KT;
@@ -280,6 +302,7 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
       const bool ok = key0 + key < kend;
       cp_async16(ks + (uint32_t)(key * KROW + ((ch ^ (key & 7)) << 4)), kbase + (int64_t)(key0 + (ok ? key : 0)) * DK + ch * 8, ok);
     }
+    if (same_kv) return;
 #pragma unroll
     for (int i = 0; i < ST_KT * VCH / NT; ++i) {
       const int idx = i * NT + threadIdx.x;
@@ -306,7 +329,7 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
-    const uint32_t ks = sbase + stage * STAGE_BYTES, vs = ks + K_BYTES;
+    const uint32_t ks = sbase + stage * STAGE_BYTES, vs = same_kv ? ks : ks + K_BYTES;
     const int key0 = it * ST_KT;
     const int mat = lane >> 3, r = lane & 7;
     float sc[ST_KT / 8][4];
@@ -331,10 +354,10 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
       if constexpr (RULED) {
         const int d00 = pos0 - kcol, d01 = d00 - 1, d10 = pos1 - kcol, d11 = d10 - 1;
         const int wnd = rule.window > 0 ? rule.window : 0x7fffffff;
-        sc[nt][0] = (d00 >= 0 && d00 < wnd) ? ruled_score(sc[nt][0], rule, r1_0, r2_0, (float)d00) : -INFINITY;
-        sc[nt][1] = (d01 >= 0 && d01 < wnd) ? ruled_score(sc[nt][1], rule, r1_0, r2_0, (float)d01) : -INFINITY;
-        sc[nt][2] = (d10 >= 0 && d10 < wnd) ? ruled_score(sc[nt][2], rule, r1_1, r2_1, (float)d10) : -INFINITY;
-        sc[nt][3] = (d11 >= 0 && d11 < wnd) ? ruled_score(sc[nt][3], rule, r1_1, r2_1, (float)d11) : -INFINITY;
+        sc[nt][0] = (d00 >= 0 && d00 < wnd) ? ruled_score_fast(sc[nt][0], rule, two_inv_cap, r1_0, r2_0, d00, ptab) : -INFINITY;
+        sc[nt][1] = (d01 >= 0 && d01 < wnd) ? ruled_score_fast(sc[nt][1], rule, two_inv_cap, r1_0, r2_0, d01, ptab) : -INFINITY;
+        sc[nt][2] = (d10 >= 0 && d10 < wnd) ? ruled_score_fast(sc[nt][2], rule, two_inv_cap, r1_1, r2_1, d10, ptab) : -INFINITY;
+        sc[nt][3] = (d11 >= 0 && d11 < wnd) ? ruled_score_fast(sc[nt][3], rule, two_inv_cap, r1_1, r2_1, d11, ptab) : -INFINITY;
       }
       sc[nt][0] = kcol <= pos0 ? fmaf(sc[nt][0], LOG2E, -slope2_0 * (float)(pos0 - kcol)) : -INFINITY;
       sc[nt][1] = kcol + 1 <= pos0 ? fmaf(sc[nt][1], LOG2E, -slope2_0 * (float)(pos0 - kcol - 1)) : -INFINITY;
@@ -413,8 +436,8 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
     const int c = 8 * j + 2 * qc;
     float a0 = o[j][0] * inv0, a1 = o[j][1] * inv0, b0 = o[j][2] * inv1, b1 = o[j][3] * inv1;
     if (RULED && g0) {
-      if (l0 < n_e) { a0 *= sigmoid_f(g0[c]); a1 *= sigmoid_f(g0[c + 1]); }
-      if (l1 < n_e) { b0 *= sigmoid_f(g1[c]); b1 *= sigmoid_f(g1[c + 1]); }
+      if (l0 < n_e) { a0 *= sigmoid_fast(g0[c]); a1 *= sigmoid_fast(g0[c + 1]); }
+      if (l1 < n_e) { b0 *= sigmoid_fast(g1[c]); b1 *= sigmoid_fast(g1[c + 1]); }
     }
     if (l0 < n_e) *reinterpret_cast<uint32_t*>(o0 + c) = pack2<T>(a0, a1);
     if (l1 < n_e) *reinterpret_cast<uint32_t*>(o1 + c) = pack2<T>(b0, b1);
@@ -450,21 +473,26 @@ __global__ void sink_attn_merge_kernel(const float* __restrict__ part_o, const f
 }
 
 constexpr int SINK_ATTN_MAX_SPLITS = 16;
+constexpr int SINK_ATTN_MAX_TABLE = 16384;      // longest window whose penalties sit in shared memory (64 KB)
 
 template <typename T, int DK, int DV, bool RULED>
 static int sink_attn_tiles_launch(const float* q, const void* kc, const void* vc, int64_t Tcap, const int32_t* cu, const int32_t* rows,
                                   const int32_t* t_pos, const float* sink, float slope_log2, void* out, int64_t ld_out,
                                   float out_scale, int nb, int max_n, int H, int G, float* ws, size_t ws_bytes, cudaStream_t st,
-                                  const ScoreRule& rule) {
-  constexpr int smem = ST_STAGES * ST_KT * (DK + DV) * 2;
+                                  const ScoreRule& rule_in) {
+  constexpr int stage_smem = ST_STAGES * ST_KT * (DK + DV) * 2;
+  // prompts with a window and a penalty: a table of the penalties of the distances 0 .. window - 1 behind the tile buffers
+  ScoreRule rule = rule_in;
+  rule.table = (RULED && max_n > 1 && rule.r1 && rule.window > 0 && rule.window <= SINK_ATTN_MAX_TABLE) ? rule.window : 0;
+  const int smem = stage_smem + rule.table * (int)sizeof(float);
   if (max_n == 1) {
     // decode: shares of the key tiles per (entry, key/value head), as many as keep several CTAs per SM busy and the workspace holds
     auto kern = sink_attn_tile_kernel<T, DK, DV, true, RULED>;
-    static bool attr_set = false;
-    if (smem > 48 * 1024 && !attr_set) {
+    static int attr_smem = 48 * 1024;
+    if (smem > attr_smem) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(sink_attn_tile_kernel)");
-      attr_set = true;
+      attr_smem = smem;
     }
     const size_t per_split = (size_t)nb * H * (DV + 2) * sizeof(float);
     int splits = (int)((8 * 148 + (int64_t)nb * G - 1) / ((int64_t)nb * G));
@@ -483,13 +511,11 @@ static int sink_attn_tiles_launch(const float* q, const void* kc, const void* vc
     return B200P_OK;
   }
   auto kern = sink_attn_tile_kernel<T, DK, DV, false, RULED>;
-  if (smem > 48 * 1024) {
-    static bool attr_set = false;
-    if (!attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-      if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(sink_attn_tile_kernel)");
-      attr_set = true;
-    }
+  static int attr_smem = 48 * 1024;                             // the table's size varies with the window: keep the largest asked for
+  if (smem > attr_smem) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(sink_attn_tile_kernel)");
+    attr_smem = smem;
   }
   dim3 grid((unsigned)((max_n + ST_QT - 1) / ST_QT), (unsigned)H, (unsigned)nb);
   kern<<<grid, ST_THREADS, smem, st>>>(q, (const T*)kc, (const T*)vc, Tcap, cu, rows, t_pos, sink, slope_log2, (T*)out, ld_out,
@@ -508,7 +534,7 @@ static int sink_attn_tiles(const float* q, const void* kc, const void* vc, int64
                            const int32_t* t_pos, const float* sink, float slope_log2, void* out, int64_t ld_out, float out_scale,
                            int nb, int max_n, int H, int G, int dk, int dv, float* ws, size_t ws_bytes, cudaStream_t st,
                            const ScoreRule* rule) {
-  static const ScoreRule none = {0.f, nullptr, nullptr, 0, nullptr, 0};
+  static const ScoreRule none = {0.f, nullptr, nullptr, 0, nullptr, 0, 0};
 #define ST_CASE(DK_, DV_) \
   if (dk == DK_ && dv == DV_ && !rule) \
     return sink_attn_tiles_launch<T, DK_, DV_, false>(q, kc, vc, Tcap, cu, rows, t_pos, sink, slope_log2, out, ld_out, out_scale, nb, max_n, H, G, ws, ws_bytes, st, none)
@@ -552,7 +578,7 @@ template <typename T>
 static int sink_attn_generic(const float* q, const void* kcache, const void* vcache, int64_t Tcap, const int32_t* t_row,
                              const int32_t* t_pos, const float* sink, float slope_log2, void* out, int64_t ld_out, float out_scale,
                              int64_t M, int H, int G, int dk, int dv, cudaStream_t st, const ScoreRule* rule = nullptr) {
-  static const ScoreRule none = {0.f, nullptr, nullptr, 0, nullptr, 0};
+  static const ScoreRule none = {0.f, nullptr, nullptr, 0, nullptr, 0, 0};
   const int per = H / G, nw = per < SA_MAX_HEADS ? per : SA_MAX_HEADS;
   const size_t smem = ((size_t)SA_KEYS * (dk + 1) + (size_t)SA_KEYS * dv + (size_t)nw * dk) * sizeof(float);
   auto kern = sink_attn_kernel<T>;
@@ -636,7 +662,7 @@ extern "C" int b200p_window_attn(const float* q, const void* kcache, const void*
   B200P_REQUIRE((r1 == nullptr) == (r2 == nullptr), B200P_ERR_ARG, "the distance penalty needs both of its vectors");
   B200P_REQUIRE(window >= 0 && window < 0x7fffffff && softcap >= 0.f, B200P_ERR_ARG, "bad window or cap");
   B200P_REQUIRE(gate == nullptr || ldg >= (int64_t)H * dv, B200P_ERR_ARG, "gate rows are shorter than the heads");
-  const ScoreRule rule = {softcap, r1, r2, (int)window, gate, ldg};
+  const ScoreRule rule = {softcap, r1, r2, (int)window, gate, ldg, 0};
   return attn_dispatch(q, kcache, vcache, Tcap, t_row, t_pos, cu, rows, nb, max_n, nullptr, 0.f, out, ld_out, 1.f, M, H, G, dk, dv, dtype,
                        workspace, workspace_bytes, stream, &rule);
 }

@@ -562,7 +562,7 @@ class WindowAttention:
         self.n_proj = self.conv_channels + (self.n_mix if gated else 0)
         self.in_proj = Linear(width, self.n_proj)
         self.o_proj = Linear(self.n_mix, width)
-        self.conv_w = self.r1 = self.r2 = None                 # fp32
+        self.conv_w = self.r1 = self.r2 = None                 # fp32; the taps tap by tap: [taps, (heads + kv_heads) * dim]
 
     def new_state(self, batch_size: int) -> RowState:
         return StateGroup([BatchedKVCache(self.dim, self.kv_heads, batch_size, values_are_keys=True),
@@ -786,7 +786,8 @@ class LayerRun:
 
 class StreamPort:
     """How one sublayer of a "hyper" model meets the copies of the residual stream: it reads u = sum_s read[s] x_s, norms it with
-    tanh(alpha u) w + b, adds the causal convolution ``conv_w`` [width, taps] of that over time, and its output y is written back
+    tanh(alpha u) w + b, adds the causal convolution ``conv_w`` (kept tap by tap, [taps, width]) of that over time, and its output y is
+    written back
     as x_r <- sum_s mix[s, r] x_s + out[r] y.  All fp32 on the device."""
 
     def __init__(self, norm_name: str, hc_name: str, conv_name: str):

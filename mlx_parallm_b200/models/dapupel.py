@@ -204,7 +204,7 @@ class Model(SequenceModel):
         def port(p: StreamPort):
             p.alpha, p.w, p.b = tanh_norm(p.norm_name)
             p.read, p.out, p.mix = vec(p.hc_name + ".in", (S,)), vec(p.hc_name + ".out", (S,)), vec(p.hc_name + ".mix", (S, S))
-            p.conv_w = vec(p.conv_name, (W, taps))
+            p.conv_w = vec(p.conv_name, (W, taps)).t().contiguous()          # tap by tap: [taps, W]
 
         check("embed", (a.vocab, W))
         self.embed.weight = put(weights["embed"])
@@ -258,7 +258,7 @@ class Model(SequenceModel):
                 check(p + "k.conv", (m.kv_heads * m.dim, m.taps))
                 m.in_proj.weight = put(torch.cat([weights[p + n] for n in ("q", "k", "g")], 0))
                 m.o_proj.weight = put(weights[p + "o"])
-                m.conv_w = torch.cat([weights[p + "q.conv"].float(), weights[p + "k.conv"].float()], 0).to(device).contiguous()
+                m.conv_w = torch.cat([weights[p + "q.conv"].float(), weights[p + "k.conv"].float()], 0).t().to(device).contiguous()   # [taps, C]
                 m.r1, m.r2 = vec(p + "r1", (m.heads,)), vec(p + "r2", (m.heads,))
             ff = r.mlp
             if ff is None:

@@ -596,7 +596,7 @@ def window_attn_prep(proj, col_q, conv_w, conv_state, taps, scale, q_out, kcache
     _dev(proj, conv_w, conv_state, q_out, kcache, t_row, t_pos, t_off)
     M = proj.shape[0]
     assert proj.dtype == torch.float32 and proj.stride(1) == 1 and kcache.is_contiguous() and q_out.is_contiguous()
-    assert kcache.shape[1:] == (G, kcache.shape[2], dk) and conv_w.shape == ((H + G) * dk, taps)
+    assert kcache.shape[1:] == (G, kcache.shape[2], dk) and conv_w.shape == (taps, (H + G) * dk)
     _call("b200p_window_attn_prep", lambda: lib().b200p_window_attn_prep(
         _p(proj), proj.stride(0), int(col_q), _p(conv_w), _p(conv_state), int(taps), float(scale), _p(q_out), _p(kcache), kcache.shape[2],
         _p(t_row), _p(t_pos), _p(t_off), M, H, G, dk, dtype_code(kcache.dtype), _stream()))
@@ -649,7 +649,7 @@ def hyper_step(xs, streams: int, y=None, src=None, mix=None, out=None, read=None
     for t in (mix, out, read, alpha, w, b, conv_w):
         assert t is None or (t.dtype == torch.float32 and t.is_contiguous())
     assert (mix is None) == (out is None) and (mix is None or mix.numel() == streams * streams)
-    assert x_out is None or (x_out.is_contiguous() and conv_w.shape == (W, taps) and conv_state.is_contiguous())
+    assert x_out is None or (x_out.is_contiguous() and conv_w.shape == (taps, W) and conv_state.is_contiguous())
     _call("b200p_hyper_step", lambda: lib().b200p_hyper_step(
         _p(xs), _p(y), _p(src), _p(mix), _p(out), _p(read), _p(alpha), _p(w), _p(b), _p(n_out), _p(sum_out), M, int(streams), W, _p(conv_w),
         _p(conv_state), _p(t_row), _p(t_pos), int(taps), _p(x_out), dtype_code(x_out.dtype if x_out is not None else torch.float32),
@@ -657,10 +657,11 @@ def hyper_step(xs, streams: int, y=None, src=None, mix=None, out=None, read=None
 
 
 def canon_conv(n, conv_w, conv_state, t_row, t_pos, t_off, x_out, taps: int):
-    """x_out = n + causal convolution of n over time (``conv_w`` [W, taps]; ``conv_state`` [rows, taps-1, W] = earlier steps)."""
+    """x_out = n + causal convolution of n over time (``conv_w`` [taps, W], tap by tap; ``conv_state`` [rows, taps-1, W] = earlier
+    steps)."""
     _dev(n, conv_w, conv_state, t_row, t_pos, t_off, x_out)
     M, W = n.shape
-    assert n.dtype == torch.float32 and n.is_contiguous() and x_out.is_contiguous() and conv_w.shape == (W, taps) and conv_state.is_contiguous()
+    assert n.dtype == torch.float32 and n.is_contiguous() and x_out.is_contiguous() and conv_w.shape == (taps, W) and conv_state.is_contiguous()
     _call("b200p_canon_conv", lambda: lib().b200p_canon_conv(_p(n), _p(conv_w), _p(conv_state), _p(t_row), _p(t_pos), _p(t_off), _p(x_out), M,
                                                             W, int(taps), dtype_code(x_out.dtype), _stream()))
 

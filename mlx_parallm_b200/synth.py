@@ -509,3 +509,120 @@ def nifalorn_random_weights(cfg: dict, seed: int = 1234, device="cpu") -> Dict[s
             t = 1.0 + 0.02 * torch.randn(shape, generator=g, device=dev)
         out[name] = t.to(torch.bfloat16)
     return out
+
+
+# ---- Dapupel ----------------------------------------------------------------------------------------------------------------
+def dapupel_config(width: int, ff: int, n_layers: int, heads: int, head_dim: int, q_rank: int, kv_rank: int, window: int,
+                   delta_heads: int, delta_kv_heads: int, delta_dim: int, delta_vdim: int, kv_heads: Optional[int] = None,
+                   rot_dim: int = 64, experts: int = 16, top: int = 2, streams: int = 4, canon_taps: int = 4, vocab: int = 32000,
+                   taps: int = 4, **unused) -> dict:
+    """A config of the design at the sizes of a real model: layers cycle (channel-delta, latent attention with a rotated key
+    part, windowed attention over its keys), every one with routed experts whose active ones together have the hidden size
+    ``ff``; ``streams`` copies of the residual stream and an input convolution of ``canon_taps`` taps."""
+    kv_heads = kv_heads or max(1, heads // 4)
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff // top, "limit": 7.0}}
+    layers = []
+    for i in range(n_layers):
+        kind = i % 3
+        if kind == 0:
+            mixer = {"heads": delta_heads, "kv_heads": delta_kv_heads, "dim": delta_dim, "vdim": delta_vdim, "conv": taps}
+            layers.append({"type": "channel_delta", "mixer": mixer, "mlp": moe})
+        elif kind == 1:
+            mixer = {"heads": heads, "dim": head_dim, "rot_dim": rot_dim, "vdim": head_dim, "q_rank": q_rank, "kv_rank": kv_rank,
+                     "scale": (head_dim + rot_dim) ** -0.5,
+                     "rot": {"dims": rot_dim, "base": 10000.0, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+            layers.append({"type": "latent_attention", "mixer": mixer, "mlp": moe})
+        else:
+            mixer = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5, "softcap": 50.0,
+                     "mask": {"size": window}, "conv": taps}
+            layers.append({"type": "attention", "mixer": mixer, "mlp": moe})
+    return {"architecture": "Dapupel", "vocab": vocab, "width": width, "layers": layers, "norm": {"eps": 1e-6}, "streams": streams,
+            "canon": {"taps": canon_taps}}
+
+
+def dapupel_shapes(cfg: dict, rank: Optional[int] = None) -> Dict[str, tuple]:
+    """Shape of every tensor of a Dapupel checkpoint (matrices [out, in]); ``rank``: inner size of the low-rank decay and gate
+    projections (default width / 16, at least 8)."""
+    W, V, S, ct = cfg["width"], cfg["vocab"], cfg["streams"], cfg["canon"]["taps"]
+    r = rank or max(8, W // 16)
+    out = {"embed": (V, W), "final.norm": (W,), "final.norm.b": (W,), "final.norm.alpha": ()}
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.mix.", L["mixer"]
+        for q in ("1", "2") if L.get("mlp") is not None else ("1",):
+            out[f"l{i}.norm{q}"] = out[f"l{i}.norm{q}.b"] = (W,)
+            out[f"l{i}.norm{q}.alpha"] = ()
+            out[f"l{i}.hc{q}.in"] = out[f"l{i}.hc{q}.out"] = (S,)
+            out[f"l{i}.hc{q}.mix"] = (S, S)
+            out[f"l{i}.canon{q}"] = (W, ct)
+        if L["type"] == "channel_delta":
+            ck, cv, n = m["kv_heads"] * m["dim"], m["heads"] * m["vdim"], m.get("conv", 1)
+            out[p + "q"] = out[p + "k"] = (ck, W)
+            out[p + "q.conv"] = out[p + "k.conv"] = (ck, n)
+            out[p + "v"], out[p + "v.conv"] = (cv, W), (cv, n)
+            out[p + "b"], out[p + "A_log"], out[p + "norm"] = (m["heads"], W), (m["heads"],), (m["vdim"],)
+            out[p + "a1"], out[p + "a2"], out[p + "dt_bias"] = (r, W), (m["heads"] * m["dim"], r), (m["heads"] * m["dim"],)
+            out[p + "g1"], out[p + "g2"], out[p + "o"] = (r, W), (cv, r), (W, cv)
+        elif L["type"] == "latent_attention":
+            H = m["heads"]
+            out[p + "dq"], out[p + "dq.norm"], out[p + "uq"] = (m["q_rank"], W), (m["q_rank"],), (H * (m["dim"] + m["rot_dim"]), m["q_rank"])
+            out[p + "dkv"], out[p + "dkv.norm"] = (m["kv_rank"] + m["rot_dim"], W), (m["kv_rank"],)
+            out[p + "uk"], out[p + "uv"], out[p + "o"] = (H * m["dim"], m["kv_rank"]), (H * m["vdim"], m["kv_rank"]), (W, H * m["vdim"])
+        else:
+            cq, ck, n = m["heads"] * m["dim"], m.get("kv_heads", m["heads"]) * m["dim"], m.get("conv", 1)
+            out[p + "q"], out[p + "k"], out[p + "g"], out[p + "o"] = (cq, W), (ck, W), (cq, W), (W, cq)
+            out[p + "q.conv"], out[p + "k.conv"] = (cq, n), (ck, n)
+            out[p + "r1"] = out[p + "r2"] = (m["heads"],)
+        mlp = L.get("mlp")
+        if mlp is None:
+            continue
+        q = f"l{i}.mlp."
+        for e in range(mlp["router"]["experts"]):
+            out[f"{q}e{e}.gate"] = out[f"{q}e{e}.up"] = (mlp["expert"]["ff"], W)
+            out[f"{q}e{e}.down"] = (W, mlp["expert"]["ff"])
+        out[q + "router"] = (mlp["router"]["experts"], W)
+    return out
+
+
+def dapupel_random_weights(cfg: dict, seed: int = 1234, device="cpu", rank: Optional[int] = None) -> Dict[str, torch.Tensor]:
+    """bfloat16 tensors: matrices N(0, 1/in), norm weights near one with small offsets, stream weights near an even read and an
+    identity write, convolution taps N(0, 0.25) (the mixers' own with a one on the current token), decay parameters spread so that
+    channels forget at different speeds."""
+    dev = torch.device(device)
+    S = cfg["streams"]
+    out: Dict[str, torch.Tensor] = {}
+    for name, shape in dapupel_shapes(cfg, rank).items():
+        g = torch.Generator(device=dev)
+        g.manual_seed(_stable_seed(seed, name))
+        parts = name.split(".")
+        leaf = parts[-1]
+        if leaf == "alpha":
+            t = torch.full(shape, 0.5, device=dev)
+        elif len(parts) >= 2 and parts[-2].startswith("hc"):
+            if leaf == "mix":
+                t = torch.eye(S, device=dev) + 0.05 * torch.randn(shape, generator=g, device=dev)
+            elif leaf == "in":
+                t = torch.full(shape, 1.0 / S, device=dev) + 0.02 * torch.randn(shape, generator=g, device=dev)
+            else:
+                t = 1.0 + 0.05 * torch.randn(shape, generator=g, device=dev)
+        elif leaf.startswith("canon"):
+            t = torch.randn(shape, generator=g, device=dev) * 0.25
+        elif leaf == "conv":
+            t = torch.randn(shape, generator=g, device=dev) * 0.5
+            if "q" in parts or "k" in parts:
+                t[:, -1] += 1.0
+        elif leaf in ("r1", "r2"):
+            t = torch.rand(shape, generator=g, device=dev) * 0.5 + 0.05
+        elif leaf == "A_log":
+            t = torch.rand(shape, generator=g, device=dev) * 3.0 - 2.0
+        elif leaf == "dt_bias":
+            t = torch.randn(shape, generator=g, device=dev)
+        elif leaf == "b" and parts[-2].startswith("norm"):
+            t = 0.02 * torch.randn(shape, generator=g, device=dev)
+        elif len(shape) == 2:
+            t = torch.randn(shape, generator=g, device=dev) / math.sqrt(shape[1])
+            if name == "embed":
+                t = t * math.sqrt(shape[1]) * 0.5
+        else:                                   # norm weights
+            t = 1.0 + 0.02 * torch.randn(shape, generator=g, device=dev)
+        out[name] = t.to(torch.bfloat16)
+    return out

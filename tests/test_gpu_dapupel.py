@@ -111,11 +111,11 @@ def test_stream_step_prompt_and_decode(S, W, taps):
         sums = torch.zeros(M, W, device="cuda")
         kw = dict(y=yy, mix=dev(mix), out=dev(out), read=dev(read), alpha=dev(alpha), w=dev(w), b=dev(b), sum_out=sums)
         if cnt == 1:
-            ops.hyper_step(xs, S, conv_w=dev(cw), conv_state=state, t_row=t_row, t_pos=t_pos, taps=taps, x_out=x_out, **kw)
+            ops.hyper_step(xs, S, conv_w=dev(cw.t()), conv_state=state, t_row=t_row, t_pos=t_pos, taps=taps, x_out=x_out, **kw)
         else:
             nn = torch.zeros(M, W, device="cuda")
             ops.hyper_step(xs, S, n_out=nn, **kw)
-            ops.canon_conv(nn, dev(cw), state, t_row, t_pos, t_off, x_out, taps)
+            ops.canon_conv(nn, dev(cw.t()), state, t_row, t_pos, t_off, x_out, taps)
             if taps > 1:
                 ops.delta_conv_commit(nn, state, torch.tensor([0, cnt, 2 * cnt], **I32), torch.tensor([2, 0], **I32), 2, W, taps)
         got_x[:, lo:lo + cnt] = x_out.cpu().view(2, cnt, W)
