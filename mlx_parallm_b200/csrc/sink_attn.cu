@@ -40,9 +40,12 @@ __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-
 // The same rule on the special-function unit, for the 16-bit tile kernel whose probabilities are rounded to 16 bits anyway:
 // tanh x = 1 - 2 / (1 + e^2x) (absolute error near 1e-7, so cap tanh(s / cap) is off by about cap * 1e-7), ln through lg2.
 // The penalty of a distance comes from `tab` (filled once per CTA: a prompt tile serves one head) where there is one.
-__device__ __forceinline__ float ruled_score_fast(float s, const ScoreRule& rule, float two_inv_cap, float r1, float r2, int dist,
+// Five instructions for the cap: cap tanh(s / cap) = cap - 2 cap / (1 + 2^(s 2 log2(e) / cap)) with the constants formed once.
+__device__ __forceinline__ float ex2_approx(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float rcp_approx(float x) { float y; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float ruled_score_fast(float s, const ScoreRule& rule, float k_exp, float cap2, float r1, float r2, int dist,
                                                   const float* tab) {
-  if (rule.cap > 0.f) s = rule.cap * (1.f - __fdividef(2.f, 1.f + __expf(s * two_inv_cap)));
+  if (rule.cap > 0.f) s = fmaf(-cap2, rcp_approx(1.f + ex2_approx(s * k_exp)), rule.cap);
   if (tab) s -= tab[dist];
   else if (rule.r1) s -= r1 * __logf(fmaf(r2, (float)dist, 1.f));
   return s;
@@ -180,7 +183,7 @@ sink_attn_kernel(const float* __restrict__ q, const T* __restrict__ kcache, cons
 // q and k of the windowed attention: projections [q (H dk) | k (G dk)] from column col_q of proj pass a causal convolution over
 // time (conv_w [taps, C], tap by tap, the last tap the current token's; conv_state [rows, taps-1, C] the inputs of earlier steps, zeros before the
 // sequence's start); q_out = that * scale (fp32), the keys go to the cache.
-template <typename T>
+template <typename T, int V>
 __global__ void window_attn_prep_kernel(const float* __restrict__ proj, int64_t ldp, int64_t col_q, const float* __restrict__ conv_w,
                                         const float* __restrict__ conv_state, int taps, float scale, float* __restrict__ q_out,
                                         T* __restrict__ kcache, int64_t Tcap, const int32_t* __restrict__ t_row,
@@ -189,20 +192,31 @@ __global__ void window_attn_prep_kernel(const float* __restrict__ proj, int64_t 
   const int C = (H + G) * dk, Cq = H * dk;
   const int row = t_row[t], pos = t_pos[t], off = t_off[t];
   const float* pt = proj + t * ldp + col_q;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    float acc = 0.f;
+  // V neighbouring channels per thread (V == 4: 16-byte accesses; the channels of a thread then lie in one head)
+  for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * V; c < C; c += gridDim.y * blockDim.x * V) {
+    float acc[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) acc[k] = 0.f;
     for (int j = 0; j < taps; ++j) {                 // tap j multiplies the input d = taps-1-j tokens back
       const int d = taps - 1 - j;
-      float in;
-      if (d > pos) in = 0.f;
-      else if (d <= off) in = pt[c - (int64_t)d * ldp];
-      else in = conv_state[((int64_t)row * (taps - 1) + (taps - 1 + off - d)) * C + c];
-      acc = fmaf(conv_w[(int64_t)j * C + c], in, acc);
+      if (d > pos) continue;                         // before the sequence
+      const float* in = d <= off ? pt + c - (int64_t)d * ldp : conv_state + ((int64_t)row * (taps - 1) + (taps - 1 + off - d)) * C + c;
+      const float* wt = conv_w + (int64_t)j * C + c;
+      if constexpr (V == 4) {
+        const float4 a = *reinterpret_cast<const float4*>(in), w4 = *reinterpret_cast<const float4*>(wt);
+        acc[0] = fmaf(w4.x, a.x, acc[0]); acc[1] = fmaf(w4.y, a.y, acc[1]); acc[2] = fmaf(w4.z, a.z, acc[2]); acc[3] = fmaf(w4.w, a.w, acc[3]);
+      } else {
+        acc[0] = fmaf(wt[0], in[0], acc[0]);
+      }
     }
-    if (c < Cq) q_out[t * Cq + c] = acc * scale;
-    else if (pos < Tcap) {                           // the host sizes the cache first; never write outside it
+    if (c < Cq) {
+      if constexpr (V == 4) *reinterpret_cast<float4*>(q_out + t * Cq + c) = make_float4(acc[0] * scale, acc[1] * scale, acc[2] * scale, acc[3] * scale);
+      else q_out[t * Cq + c] = acc[0] * scale;
+    } else if (pos < Tcap) {                         // the host sizes the cache first; never write outside it
       const int g = (c - Cq) / dk, i = (c - Cq) % dk;
-      kcache[(((int64_t)row * G + g) * Tcap + pos) * dk + i] = Tr<T>::from_f(acc);
+      T* dst = kcache + (((int64_t)row * G + g) * Tcap + pos) * dk + i;
+#pragma unroll
+      for (int k = 0; k < V; ++k) dst[k] = Tr<T>::from_f(acc[k]);
     }
   }
 }
@@ -223,7 +237,7 @@ constexpr float LOG2E = 1.4426950408889634f;
 // RULED = true: the scores also pass the ScoreRule (cap, logarithmic penalty, window: tiles before the window of the CTA's first
 // row are skipped, a row whose window has not begun keeps max = -inf and adds nothing) and the output its gate.
 template <typename T, int DK, int DV, bool DECODE, bool RULED>
-__global__ void __launch_bounds__(DECODE ? 32 : ST_THREADS)
+__global__ void __launch_bounds__(DECODE ? 32 : ST_THREADS, (RULED && !DECODE) ? 3 : 1)
 sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, const T* __restrict__ vc, int64_t Tcap,
                       const int32_t* __restrict__ cu, const int32_t* __restrict__ rows, const int32_t* __restrict__ t_pos,
                       const float* __restrict__ sink, float slope_log2, T* __restrict__ out, int64_t ld_out, float out_scale,
@@ -262,11 +276,15 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
   }
   float r1_0 = 0.f, r2_0 = 0.f, r1_1 = 0.f, r2_1 = 0.f;
   if (RULED && rule.r1) { r1_0 = rule.r1[h0]; r2_0 = rule.r2[h0]; r1_1 = rule.r1[h1]; r2_1 = rule.r2[h1]; }
-  const float two_inv_cap = (RULED && rule.cap > 0.f) ? 2.f / rule.cap : 0.f;
+  const float k_exp = (RULED && rule.cap > 0.f) ? 2.f * LOG2E / rule.cap : 0.f, cap2 = 2.f * rule.cap;
+  // values that are the keys (one buffer, equal sizes): the staged key tile serves both products, no value tile is loaded and a
+  // stage is half as large (the launcher sizes the shared memory accordingly)
+  const bool same_kv = RULED && DK == DV && kc == vc;
+  const int stage_bytes = same_kv ? K_BYTES : STAGE_BYTES;
   const float* ptab = nullptr;
   if (RULED && !DECODE && rule.r1 && rule.table > 0) {
     // every distance a visible pair of this CTA can have (below the window) once, instead of a logarithm per score
-    float* tab = reinterpret_cast<float*>(st_smem + ST_STAGES * (ST_KT * (DK + DV) * 2));
+    float* tab = reinterpret_cast<float*>(st_smem + ST_STAGES * stage_bytes);
     for (int i = threadIdx.x; i < rule.table; i += NT) tab[i] = r1_0 * __logf(fmaf(r2_0, (float)i, 1.f));
     ptab = tab;                                                     // read after the first tile's __syncthreads
   }
@@ -290,10 +308,8 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
   const int64_t row = rows[e];
   const T* kbase = kc + (row * G + g) * Tcap * DK;
   const T* vbase = vc + (row * G + g) * Tcap * DV;
-  // values that are the keys (one buffer, equal sizes): the staged key tile serves both products and no value tile is loaded
-  const bool same_kv = RULED && DK == DV && kc == vc;
   auto issue_tile = [&](int tile, int stage) {
-    const uint32_t ks = sbase + stage * STAGE_BYTES, vs = ks + K_BYTES;
+    const uint32_t ks = sbase + stage * stage_bytes, vs = ks + K_BYTES;
     const int key0 = tile * ST_KT;
 #pragma unroll
     for (int i = 0; i < ST_KT * KCH / NT; ++i) {
@@ -329,7 +345,7 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
-    const uint32_t ks = sbase + stage * STAGE_BYTES, vs = same_kv ? ks : ks + K_BYTES;
+    const uint32_t ks = sbase + stage * stage_bytes, vs = same_kv ? ks : ks + K_BYTES;
     const int key0 = it * ST_KT;
     const int mat = lane >> 3, r = lane & 7;
     float sc[ST_KT / 8][4];
@@ -354,15 +370,19 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
       if constexpr (RULED) {
         const int d00 = pos0 - kcol, d01 = d00 - 1, d10 = pos1 - kcol, d11 = d10 - 1;
         const int wnd = rule.window > 0 ? rule.window : 0x7fffffff;
-        sc[nt][0] = (d00 >= 0 && d00 < wnd) ? ruled_score_fast(sc[nt][0], rule, two_inv_cap, r1_0, r2_0, d00, ptab) : -INFINITY;
-        sc[nt][1] = (d01 >= 0 && d01 < wnd) ? ruled_score_fast(sc[nt][1], rule, two_inv_cap, r1_0, r2_0, d01, ptab) : -INFINITY;
-        sc[nt][2] = (d10 >= 0 && d10 < wnd) ? ruled_score_fast(sc[nt][2], rule, two_inv_cap, r1_1, r2_1, d10, ptab) : -INFINITY;
-        sc[nt][3] = (d11 >= 0 && d11 < wnd) ? ruled_score_fast(sc[nt][3], rule, two_inv_cap, r1_1, r2_1, d11, ptab) : -INFINITY;
+        sc[nt][0] = (d00 >= 0 && d00 < wnd) ? ruled_score_fast(sc[nt][0], rule, k_exp, cap2, r1_0, r2_0, d00, ptab) : -INFINITY;
+        sc[nt][1] = (d01 >= 0 && d01 < wnd) ? ruled_score_fast(sc[nt][1], rule, k_exp, cap2, r1_0, r2_0, d01, ptab) : -INFINITY;
+        sc[nt][2] = (d10 >= 0 && d10 < wnd) ? ruled_score_fast(sc[nt][2], rule, k_exp, cap2, r1_1, r2_1, d10, ptab) : -INFINITY;
+        sc[nt][3] = (d11 >= 0 && d11 < wnd) ? ruled_score_fast(sc[nt][3], rule, k_exp, cap2, r1_1, r2_1, d11, ptab) : -INFINITY;
       }
-      sc[nt][0] = kcol <= pos0 ? fmaf(sc[nt][0], LOG2E, -slope2_0 * (float)(pos0 - kcol)) : -INFINITY;
-      sc[nt][1] = kcol + 1 <= pos0 ? fmaf(sc[nt][1], LOG2E, -slope2_0 * (float)(pos0 - kcol - 1)) : -INFINITY;
-      sc[nt][2] = kcol <= pos1 ? fmaf(sc[nt][2], LOG2E, -slope2_1 * (float)(pos1 - kcol)) : -INFINITY;
-      sc[nt][3] = kcol + 1 <= pos1 ? fmaf(sc[nt][3], LOG2E, -slope2_1 * (float)(pos1 - kcol - 1)) : -INFINITY;
+      if (RULED && slope_log2 == 0.f) {                            // masked above; no linear bias: the scores just move to base 2
+        sc[nt][0] *= LOG2E; sc[nt][1] *= LOG2E; sc[nt][2] *= LOG2E; sc[nt][3] *= LOG2E;
+      } else {
+        sc[nt][0] = kcol <= pos0 ? fmaf(sc[nt][0], LOG2E, -slope2_0 * (float)(pos0 - kcol)) : -INFINITY;
+        sc[nt][1] = kcol + 1 <= pos0 ? fmaf(sc[nt][1], LOG2E, -slope2_0 * (float)(pos0 - kcol - 1)) : -INFINITY;
+        sc[nt][2] = kcol <= pos1 ? fmaf(sc[nt][2], LOG2E, -slope2_1 * (float)(pos1 - kcol)) : -INFINITY;
+        sc[nt][3] = kcol + 1 <= pos1 ? fmaf(sc[nt][3], LOG2E, -slope2_1 * (float)(pos1 - kcol - 1)) : -INFINITY;
+      }
       t0 = fmaxf(t0, fmaxf(sc[nt][0], sc[nt][1]));
       t1 = fmaxf(t1, fmaxf(sc[nt][2], sc[nt][3]));
     }
@@ -480,7 +500,7 @@ static int sink_attn_tiles_launch(const float* q, const void* kc, const void* vc
                                   const int32_t* t_pos, const float* sink, float slope_log2, void* out, int64_t ld_out,
                                   float out_scale, int nb, int max_n, int H, int G, float* ws, size_t ws_bytes, cudaStream_t st,
                                   const ScoreRule& rule_in) {
-  constexpr int stage_smem = ST_STAGES * ST_KT * (DK + DV) * 2;
+  const int stage_smem = ST_STAGES * ST_KT * ((RULED && DK == DV && kc == vc) ? DK : DK + DV) * 2;
   // prompts with a window and a penalty: a table of the penalties of the distances 0 .. window - 1 behind the tile buffers
   ScoreRule rule = rule_in;
   rule.table = (RULED && max_n > 1 && rule.r1 && rule.window > 0 && rule.window <= SINK_ATTN_MAX_TABLE) ? rule.window : 0;
@@ -648,8 +668,18 @@ extern "C" int b200p_window_attn_prep(const float* proj, int64_t ldp, int64_t co
   B200P_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && taps >= 1 && (taps == 1 || conv_state), B200P_ERR_ARG,
                 "bad head geometry, or a convolution without its carried inputs");
   if (M == 0) return B200P_OK;
-  B200P_DISPATCH_DTYPE(dtype, T, (window_attn_prep_kernel<T><<<(unsigned)M, 256, 0, (cudaStream_t)stream>>>(
-      proj, ldp, col_q, conv_w, conv_state, taps, scale, q_out, (T*)kcache, Tcap, t_row, t_pos, t_off, H, G, dk)));
+  const int C = (H + G) * dk;
+  const bool vec = dk % 4 == 0 && ldp % 4 == 0 && col_q % 4 == 0 && aligned(proj, 16) && aligned(conv_w, 16) && aligned(q_out, 16) &&
+                   (taps == 1 || aligned(conv_state, 16));
+  const int per = vec ? C / 4 : C;
+  const dim3 grid((unsigned)M, M >= 512 ? 1u : (unsigned)((per + 255) / 256 > 8 ? 8 : (per + 255) / 256));
+  if (vec) {
+    B200P_DISPATCH_DTYPE(dtype, T, (window_attn_prep_kernel<T, 4><<<grid, 256, 0, (cudaStream_t)stream>>>(
+        proj, ldp, col_q, conv_w, conv_state, taps, scale, q_out, (T*)kcache, Tcap, t_row, t_pos, t_off, H, G, dk)));
+  } else {
+    B200P_DISPATCH_DTYPE(dtype, T, (window_attn_prep_kernel<T, 1><<<grid, 256, 0, (cudaStream_t)stream>>>(
+        proj, ldp, col_q, conv_w, conv_state, taps, scale, q_out, (T*)kcache, Tcap, t_row, t_pos, t_off, H, G, dk)));
+  }
   B200P_LAUNCH_CHECK("window_attn_prep_kernel");
   return B200P_OK;
 }
