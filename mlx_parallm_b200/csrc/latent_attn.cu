@@ -150,8 +150,8 @@ latent_attn_kernel(const float* __restrict__ q, const T* __restrict__ cache, int
     }
     const float cmx = warp_max(s);
     const float nmx = fmaxf(mx, cmx);
-    const float corr = __expf(mx - nmx);                           // 0 on the first chunk (mx = -inf)
-    const float p = lane < nk ? __expf(s - nmx) : 0.f;
+    const float corr = expf(mx - nmx);                             // 0 on the first chunk (mx = -inf)
+    const float p = lane < nk ? expf(s - nmx) : 0.f;
     den = den * corr + warp_sum(p);
     mx = nmx;
 #pragma unroll

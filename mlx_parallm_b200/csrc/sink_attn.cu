@@ -285,7 +285,7 @@ sink_attn_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc, con
   if (RULED && !DECODE && rule.r1 && rule.table > 0) {
     // every distance a visible pair of this CTA can have (below the window) once, instead of a logarithm per score
     float* tab = reinterpret_cast<float*>(st_smem + ST_STAGES * stage_bytes);
-    for (int i = threadIdx.x; i < rule.table; i += NT) tab[i] = r1_0 * __logf(fmaf(r2_0, (float)i, 1.f));
+    for (int i = threadIdx.x; i < rule.table; i += NT) tab[i] = r1_0 * log1pf(r2_0 * (float)i);
     ptab = tab;                                                     // read after the first tile's __syncthreads
   }
   const float slope2_0 = head_slope(slope_log2, h0, H) * LOG2E, slope2_1 = head_slope(slope_log2, h1, H) * LOG2E;
