@@ -448,7 +448,7 @@ def test_batch_generate_front_end(models):
     assert len(out) == 2 and out[0] == alone[0]
 
 
-@pytest.mark.parametrize("R,window", [(32, 0), (64, 9), (96, 64), (256, 65), (512, 40)])
+@pytest.mark.parametrize("R,window", [(32, 0), (64, 9), (96, 64), (256, 65), (512, 40), (576, 0), (640, 70), (544, 64)])
 def test_latent_attention_tile_kernel(R, window):
     """The tensor-core prompt kernel against float64, on a ragged batch whose entries start at different positions of
     different cache rows (1 to 70 tokens, so tiles are full, partial and single), with a dominant key placed exactly at the
@@ -507,7 +507,7 @@ def test_latent_attention_tile_kernel(R, window):
 
 
 @pytest.mark.parametrize("splits", [0, 1, 2, 4, 8])
-@pytest.mark.parametrize("H,R,window", [(20, 64, 33), (8, 128, 0), (16, 32, 64), (3, 512, 130)])
+@pytest.mark.parametrize("H,R,window", [(20, 64, 33), (8, 128, 0), (16, 32, 64), (3, 512, 130), (9, 576, 0), (32, 640, 100)])
 def test_latent_attention_decode_tiles_over_heads(H, R, window, splits):
     """A decode step (one token per entry) tiles over the heads of each token: against float64 and against the per-token
     kernel, entries at different positions (also position 0), a head count that leaves the last tile partial.  With the keys
@@ -566,10 +566,10 @@ def test_latent_attention_tiles_sharing_keys_between_heads():
 
 
 def test_latent_attention_rank_above_the_tile_kernel():
-    """Rank 640 runs on the per-token kernel (the tile kernel stops at 512)."""
+    """Rank 672 runs on the per-token kernel (the tile kernel stops at 640)."""
     from mlx_parallm_b200 import ops
     g = torch.Generator().manual_seed(8)
-    H, R, window, T = 2, 640, 6, 19
+    H, R, window, T = 2, 672, 6, 19
     cache = (torch.randn(1, 32, R, generator=g) * 0.2).to(torch.bfloat16)
     q = torch.randn(T, H, R, generator=g) * 0.2
     i32 = dict(dtype=torch.int32, device="cuda")
