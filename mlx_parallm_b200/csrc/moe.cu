@@ -180,6 +180,16 @@ __global__ void moe_scatter_scaled_kernel(const T* __restrict__ x, const int32_t
   const float w = wts[tk];
   const T* src = x + i * W;
   T* dst = xs + (int64_t)slot_of[tk] * W;
+  if (sizeof(T) == 2 && W % 8 == 0) {                  // 16-byte pieces of eight 16-bit values (rows start on 16-byte boundaries)
+    for (int64_t c = threadIdx.x * 8; c < W; c += blockDim.x * 8) {
+      uint4 raw = *reinterpret_cast<const uint4*>(src + c);
+      T* v = reinterpret_cast<T*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = Tr<T>::from_f(w * Tr<T>::to_f(v[i]));
+      *reinterpret_cast<uint4*>(dst + c) = raw;
+    }
+    return;
+  }
   for (int64_t c = threadIdx.x; c < W; c += blockDim.x) dst[c] = Tr<T>::from_f(w * Tr<T>::to_f(src[c]));
 }
 
@@ -269,6 +279,7 @@ extern "C" int b200p_moe_route_scores(const float* logits, int64_t ldl, int32_t*
 extern "C" int b200p_moe_scatter_scaled(const void* x, const int32_t* slot_of, const float* wts, void* xs, int64_t M, int64_t W, int top,
                                         int dtype, void* stream) {
   B200P_REQUIRE(x && slot_of && wts && xs && W > 0 && top > 0 && top <= MOE_MAX_TOP, B200P_ERR_ARG, "null pointer or bad top");
+  B200P_REQUIRE(dtype == B200P_F32 || W % 8 != 0 || (aligned(x, 16) && aligned(xs, 16)), B200P_ERR_ALIGN, "x and xs must be 16-byte aligned");
   if (M == 0) return B200P_OK;
   B200P_DISPATCH_DTYPE(dtype, T, (moe_scatter_scaled_kernel<T><<<dim3((unsigned)M, (unsigned)top), 128, 0, (cudaStream_t)stream>>>(
       (const T*)x, slot_of, wts, (T*)xs, W)));
