@@ -524,7 +524,7 @@ int b200p_hyper_step(float* xs, const float* y, const float* src, const float* m
                      int64_t W, const float* conv_w, float* conv_state, const int32_t* t_row, const int32_t* t_pos, int taps,
                      void* x_out, int dtype, void* stream);
 /* The same convolution for steps of several tokens per entry: x_out (dtype) = n + conv(n) over the portion's rows of n [M, W] and,
- * before the portion, conv_state (commit it afterwards with b200p_delta_conv_commit on n). */
+ * before the portion, conv_state (commit it afterwards with b200p_delta_conv_commit on n); conv_w fp32 [taps, W] as above. */
 int b200p_canon_conv(const float* n, const float* conv_w, const float* conv_state, const int32_t* t_row, const int32_t* t_pos,
                      const int32_t* t_off, void* x_out, int64_t M, int64_t W, int taps, int dtype, void* stream);
 /* x_out (dtype [M, W]) = tanh(alpha[0] h) w + b: the norm without statistics, on given rows */

@@ -6,7 +6,7 @@
 //                       and, when every entry brings ONE token (a decode step), also the convolution over n and the carried
 //                       inputs, the storage-type result and the shift of the carried inputs -- the thread that reads a channel's
 //                       history is the one that replaces it, so nothing else has to wait
-//   canon_conv_kernel   prompts: x = n + sum_j w[:, j] n_(t - taps + 1 + j) over the portion's rows or, before its start, the
+//   canon_conv_kernel   prompts: x = n + sum_j w[j, :] n_(t - taps + 1 + j) over the portion's rows or, before its start, the
 //                       carried inputs (zeros before the sequence's start); the carried inputs are committed afterwards by
 //                       b200p_delta_conv_commit on n.  The taps are stored tap by tap, [taps, W], so that a thread's channels
 //                       are neighbours in memory
